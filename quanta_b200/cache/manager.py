@@ -118,24 +118,32 @@ class RequestRecord:
 
 
 class CacheManager:
-    def __init__(self, needs: list[CacheSpec | None], page_size: int, num_pages: int, max_requests: int):
-        """``needs[pos]``: what schedule position ``pos`` keeps (None: nothing).  Every group gets
-        ``num_pages`` pages of ``page_size`` tokens."""
+    def __init__(self, needs: list, page_size: int, num_pages: int, max_requests: int):
+        """``needs[pos]``: what schedule position ``pos`` keeps: a ``CacheSpec``, a tuple of them, or None for
+        nothing.  Every group gets ``num_pages`` pages of ``page_size`` rows; a group whose rows stand for
+        ``stride`` tokens each gets ``ceil(num_pages / stride) + max_requests`` (every request may leave one page
+        partly filled)."""
         if page_size <= 0 or num_pages <= 0 or max_requests <= 0:
             raise ValueError("page_size, num_pages and max_requests must be positive")
         self.page_size = int(page_size)
         self.groups: list[CacheGroup] = []
-        self.group_of: dict[int, int] = {}
+        self.group_of: dict[int, int] = {}             # schedule position -> the group of its first spec
+        self.groups_of: dict[int, list[int]] = {}      # schedule position -> the groups of all its specs
         by_spec: dict[CacheSpec, int] = {}
-        for pos, spec in enumerate(needs):
-            if spec is None:
+        for pos, need in enumerate(needs):
+            if need is None:
                 continue
-            if spec not in by_spec:
-                by_spec[spec] = len(self.groups)
-                self.groups.append(CacheGroup(spec, [], PagePool(num_pages)))
-            g = by_spec[spec]
-            self.groups[g].positions.append(pos)
-            self.group_of[pos] = g
+            for spec in (need if isinstance(need, (tuple, list)) else (need,)):
+                if spec.stride < 1:
+                    raise ValueError(f"a cache spec's stride is {spec.stride}; it counts tokens per row")
+                if spec not in by_spec:
+                    by_spec[spec] = len(self.groups)
+                    pages = num_pages if spec.stride == 1 else -(-num_pages // spec.stride) + max_requests
+                    self.groups.append(CacheGroup(spec, [], PagePool(pages)))
+                g = by_spec[spec]
+                self.groups[g].positions.append(pos)
+                self.groups_of.setdefault(pos, []).append(g)
+            self.group_of[pos] = self.groups_of[pos][0]
         self.slots = SlotPool(max_requests)
         self.requests: dict = {}
         self.preemptions = 0
@@ -165,8 +173,11 @@ class CacheManager:
     def pages_needed(self, rid, new_length: int) -> list[int]:
         """New pages each group must get so that positions ``[0, new_length)`` can be written (a
         request the manager does not know yet holds none)."""
-        want_pages = -(-new_length // self.page_size)
-        return [max(0, want_pages - len(g.tables.get(rid, ()))) for g in self.groups]
+        out = []
+        for g in self.groups:
+            rows = -(-new_length // g.spec.stride)          # a group may keep one row per `stride` tokens
+            out.append(max(0, -(-rows // self.page_size) - len(g.tables.get(rid, ()))))
+        return out
 
     def can_reserve(self, wants: dict) -> bool:
         """``wants``: request id -> new length.  True if every group can serve all of them together."""
@@ -212,7 +223,7 @@ class CacheManager:
         """Give back the pages of ``rid`` that no query at a position >= ``length`` reads.  The last range
         of the rule is open-ended and only moves forward; pages it has passed are looked at once when it
         passes them and again only while an earlier (closed) range still holds them."""
-        ps = self.page_size
+        ps = self.page_size * g.spec.stride            # positions a page covers
         ranges = g.spec.retention.needed_ranges(length)
         if not ranges or ranges[-1][1] is not None:
             raise ValueError(f"{type(g.spec.retention).__name__}.needed_ranges must end with an open range")

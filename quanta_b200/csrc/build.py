@@ -37,6 +37,8 @@ UNITS = {
     "recurrent": ["short_conv.cu", "delta_rule.cu"],
     "latent": ["latent_attention.cu"],
     "linear_attention": ["gla.cu"],
+    "window_attention": ["window_attention.cu"],
+    "state_space": ["selective_scan.cu"],
 }
 
 

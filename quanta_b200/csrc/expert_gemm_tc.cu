@@ -502,13 +502,15 @@ extern "C" int qb_gather_rows(const void* x, void* out, const int* sorted_pair, 
 // x_rows: bf16 [n_pairs, K] in sorted order (mode 1: the gathered activations; mode 2: the act rows); or,
 // mode 1 with gather_k > 0, the step's activations [n_rows, K] themselves: the kernel fetches the row of
 // token sorted_pair[p] / gather_k for pair p (one TMA box a row: for steps of few tokens).
-// weights: bf16 [E, (mode 1 ? 2 : 1) * N_out, K].  NT: token tile (16..256, a multiple of 16); the plan's
+// weights: bf16 [weight_experts, (mode 1 ? 2 : 1) * N_out, K] (weight_experts 0: E; fewer than E when the plan's
+// last experts have no weights and no tiles).  NT: token tile (16..256, a multiple of 16); the plan's
 // tile list must have been made with the same NT.
 extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weights, void* out, const int* sorted_pair,
                                  const float* pair_w, const int* plan, const int* tile_expert, const int* tile_row0,
                                  int max_tiles, int n_pairs, int E, int K, int N_out, int NT, int gather_k, int n_rows,
-                                 int* status, cudaStream_t stream) {
+                                 int* status, int weight_experts, cudaStream_t stream) {
   if (max_tiles <= 0 || n_pairs <= 0) return 0;
+  if (weight_experts <= 0 || weight_experts > E) weight_experts = E;
   if (K % 8 || K <= 0 || N_out <= 0 || NT < 16 || NT > 256 || NT % 16 || max_tiles > 65535) return QB_ERR_UNSUPPORTED;
   if (mode != 1 && mode != 2 && mode != 3) return QB_ERR_BAD_ARG;
   // weight tiles a block: gate and up (mode 1); two blocks of 128 features for the down product of 256-row
@@ -519,7 +521,7 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   const bool pair = NT == 256;
   if (((uintptr_t)x_rows | (uintptr_t)weights) & 15) return QB_ERR_BAD_ARG;
   CUtensorMap tm_w, tm_x;
-  int rc = make_map(&tm_w, weights, (uint64_t)E * (mode == 1 ? 2 : 1) * N_out, (uint64_t)K, EG_M);
+  int rc = make_map(&tm_w, weights, (uint64_t)weight_experts * (mode == 1 ? 2 : 1) * N_out, (uint64_t)K, EG_M);
   if (rc) return rc;
   if (gather_k < 0 || (gather_k > 0 && (mode == 2 || n_rows <= 0))) return QB_ERR_BAD_ARG;
   rc = gather_k > 0 ? make_map(&tm_x, x_rows, (uint64_t)n_rows, (uint64_t)K, 1u)

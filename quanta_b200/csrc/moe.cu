@@ -7,6 +7,10 @@
 //   (src/quanta/minimax/moe.py:36-56).
 //   A second way of weighting (`renorm` = QB_ROUTE_SOFTMAX_CHOSEN): choice = logits + bias, top-k by the
 //   same order, w = softmax over the chosen values only, times scale.
+//   A third (QB_ROUTE_SOFTMAX_ALL): scores = softmax(logits) over all router outputs, choice = scores + bias,
+//   w = the chosen scores as they are, times scale.  The last router outputs may stand for experts without
+//   weights that hand their input through (`tiled` experts have weights and get tiles in the plan; the pairs of
+//   the others are still counted and sorted, and identity_slots_kernel writes their results).
 //   expert e on row x: down_e( silu(gate_e x) * up_e x ), times w, summed over the k slots in slot
 //   order by the next norm kernel (src/quanta/minimax/moe.py:59-88); or, ungated (MODE 3 below),
 //   down_e( relu(up_e x)^2 ).
@@ -16,6 +20,7 @@
 #define QB_ROUTE_SIGMOID_RAW 0        // sigmoid scores as they are
 #define QB_ROUTE_SIGMOID_RENORM 1     // sigmoid scores divided by their sum
 #define QB_ROUTE_SOFTMAX_CHOSEN 2     // choice by logit + bias; softmax over the chosen values
+#define QB_ROUTE_SOFTMAX_ALL 3        // softmax over all logits; choice by score + bias; the chosen scores as they are
 
 // ---------------------------------------------------------------------------------------------
 // routing: one warp per token
@@ -42,6 +47,19 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
   const int lane = threadIdx.x & 31;
   float choice[NPL], score[NPL];
   unsigned taken = 0u;
+  float all_max = -INFINITY, all_inv = 0.f;
+  if (renorm == QB_ROUTE_SOFTMAX_ALL) {
+    // the softmax over all router outputs: maximum, then the sum in lane order, then a butterfly
+#pragma unroll
+    for (int i = 0; i < NPL; ++i)
+      if (lane + 32 * i < E) all_max = fmaxf(all_max, logit[i]);
+    all_max = qb_warp_max(all_max);
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i)
+      if (lane + 32 * i < E) part += expf(logit[i] - all_max);
+    all_inv = 1.f / qb_warp_sum(part);
+  }
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int e = lane + 32 * i;
@@ -50,6 +68,9 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
       const float x = logit[i];
       if (renorm == QB_ROUTE_SOFTMAX_CHOSEN) {
         score[i] = choice[i] = x + bias[i];
+      } else if (renorm == QB_ROUTE_SOFTMAX_ALL) {
+        score[i] = expf(x - all_max) * all_inv;
+        choice[i] = score[i] + bias[i];
       } else {
         const float s = 1.f / (1.f + expf(-x));
         score[i] = s;
@@ -99,7 +120,7 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
     }
   }
   __syncwarp();
-  const float denom = renorm == QB_ROUTE_SOFTMAX_CHOSEN ? sum : (renorm && k > 1) ? sum + 1e-20f : 1.f;
+  const float denom = renorm == QB_ROUTE_SOFTMAX_CHOSEN ? sum : (renorm == QB_ROUTE_SIGMOID_RENORM && k > 1) ? sum + 1e-20f : 1.f;
   for (int r = lane; r < k; r += 32) w_row[r] = s_score[r] / denom * scale;
 }
 
@@ -238,16 +259,16 @@ __global__ void moe_count_kernel(const int* __restrict__ idx, int n_pairs, int E
 __global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict__ offsets,
                                 int* __restrict__ num_tiles, int* __restrict__ active,
                                 int* __restrict__ tile_expert, int* __restrict__ tile_row0, int E, int BM,
-                                int max_tiles) {
+                                int max_tiles, int tiled) {
   __shared__ int s_cnt[1024];
   __shared__ int s_til[1024];
   __shared__ int s_act[1024];
   const int e = threadIdx.x;
   const int c = e < E ? counts[e] : 0;
-  const int nt = (c + BM - 1) / BM;
+  const int nt = e < tiled ? (c + BM - 1) / BM : 0;      // experts without weights get no tiles
   s_cnt[e] = c;
   s_til[e] = nt;
-  s_act[e] = c > 0;
+  s_act[e] = c > 0 && e < tiled;
   __syncthreads();
   for (int o = 1; o < 1024; o <<= 1) {
     int a = 0, b = 0, d = 0;
@@ -260,7 +281,7 @@ __global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict_
   }
   const int off = s_cnt[e] - c, toff = s_til[e] - nt;     // exclusive prefixes
   if (e < E) offsets[e] = off;
-  if (c > 0) active[s_act[e] - 1] = e;                    // experts with rows, in index order
+  if (c > 0 && e < tiled) active[s_act[e] - 1] = e;       // experts with rows, in index order
   if (e == E - 1) { offsets[E] = s_cnt[e]; num_tiles[0] = min(s_til[e], max_tiles); num_tiles[1] = s_act[e]; }
   for (int i = 0; i < nt; ++i) {
     if (toff + i < max_tiles) {
@@ -296,7 +317,7 @@ template <int NTH, bool IDX_SHARED = false, typename Sync>
 __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int E, int BM, int* __restrict__ plan,
                                                 int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
                                                 int* __restrict__ tile_row0, int max_tiles, int* status,
-                                                PlanShared& sh, Sync sync) {
+                                                PlanShared& sh, Sync sync, int tiled) {
   int* s_cur = sh.cur;
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   s_cur[e] = 0;
@@ -308,8 +329,8 @@ __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int
   }
   sync();
   const int c = e < E ? s_cur[e] : 0;
-  const int nt = (c + BM - 1) / BM;
-  int sc = c, st = nt, sa = c > 0;             // inclusive sums over the experts up to e
+  const int nt = e < tiled ? (c + BM - 1) / BM : 0;      // experts without weights get no tiles
+  int sc = c, st = nt, sa = c > 0 && e < tiled;             // inclusive sums over the experts up to e
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int a = __shfl_up_sync(0xffffffffu, sc, o), b = __shfl_up_sync(0xffffffffu, st, o),
@@ -325,7 +346,7 @@ __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int
   int* num_tiles = plan + 3 * E + 1;
   int* active = plan + 3 * E + 4;
   if (e < E) { counts[e] = c; offsets[e] = off; }
-  if (c > 0) active[sa - 1] = e;
+  if (c > 0 && e < tiled) active[sa - 1] = e;
   if (e == E - 1) { offsets[E] = sc; num_tiles[0] = min(st, max_tiles); num_tiles[1] = sa; }
   for (int i = 0; i < nt; ++i) {
     if (toff + i < max_tiles) {
@@ -345,10 +366,10 @@ __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int
 __global__ void __launch_bounds__(1024)
 moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, int E, int BM, int* __restrict__ plan,
                       int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
-                      int* __restrict__ tile_row0, int max_tiles, int* status) {
+                      int* __restrict__ tile_row0, int max_tiles, int* status, int tiled) {
   __shared__ PlanShared sh;
   plan_small_body<1024>(idx, n_pairs, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh,
-                        [] { __syncthreads(); });
+                        [] { __syncthreads(); }, tiled);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -385,7 +406,7 @@ router_small_kernel(const TX* __restrict__ x, const float* __restrict__ gate, co
                     float* logits, int* idx_out, float* __restrict__ w_out, int T, int E, int K, int k, int renorm,
                     float scale, int select, int* counters, int BM, int* __restrict__ plan,
                     int* __restrict__ sorted_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                    int max_tiles, int* status) {
+                    int max_tiles, int* status, int tiled) {
   constexpr int EPB = RS_WARPS / KW;                            // experts a block
   extern __shared__ __align__(16) unsigned char rs_smem[];      // [RS_TT][K] of TX: the tile's token rows
   __shared__ PlanShared sh;
@@ -547,10 +568,10 @@ router_small_kernel(const TX* __restrict__ x, const float* __restrict__ gate, co
   }
   if (gridDim.y == 1 && k <= 32)       // the step is this one tile: its choices are still in shared memory
     plan_small_body<RS_WARPS * 32, true>(s_chosen, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles,
-                                         status, sh, [] { __syncthreads(); });
+                                         status, sh, [] { __syncthreads(); }, tiled);
   else
     plan_small_body<RS_WARPS * 32>(idx_out, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh,
-                                   [] { __syncthreads(); });
+                                   [] { __syncthreads(); }, tiled);
 }
 
 // Token rows of at most this many bytes fit the shared-memory tile.
@@ -567,9 +588,10 @@ extern "C" int qb_router_small_selects(int T, int E, int k) {
 extern "C" int qb_router_small(const void* x, int x_dtype, const float* gate, const float* bias, float* logits,
                                int* idx_out, float* w_out, int T, int E, int K, int k, int renorm, float scale,
                                int select, int* counters, int BM, int* plan, int* sorted_pair, int* tile_expert,
-                               int* tile_row0, int max_tiles, int* status, cudaStream_t stream) {
+                               int* tile_row0, int max_tiles, int* status, int tiled, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E <= 0 || K <= 0) return QB_ERR_BAD_ARG;
+  if (tiled <= 0 || tiled > E) tiled = E;
   if (select && (!qb_router_small_selects(T, E, k) || counters == nullptr || k <= 0 || k > E)) return QB_ERR_BAD_ARG;
   const size_t smem = (size_t)RS_TT * K * (x_dtype == QB_F32 ? 4 : 2);
   if (smem > RS_MAX_TILE_BYTES) return QB_ERR_UNSUPPORTED;
@@ -586,7 +608,7 @@ extern "C" int qb_router_small(const void* x, int x_dtype, const float* gate, co
     if (err != cudaSuccess) return (int)err;                                                                       \
     router_small_kernel<TX, N, V, KW_><<<grid, RS_WARPS * 32, smem, stream>>>(                                     \
         (const TX*)x, gate, bias, logits, idx_out, w_out, T, E, K, k, renorm, scale, select, counters, BM, plan,  \
-        sorted_pair, tile_expert, tile_row0, max_tiles, status);                                                   \
+        sorted_pair, tile_expert, tile_row0, max_tiles, status, tiled);                                            \
   } while (0)
 #define QB_RS_K(TX, N, V)                                \
   do {                                                   \
@@ -605,13 +627,14 @@ extern "C" int qb_router_small(const void* x, int x_dtype, const float* gate, co
 }
 
 extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan, int* sorted_pair,
-                           int* tile_expert, int* tile_row0, int max_tiles, int* status,
+                           int* tile_expert, int* tile_row0, int max_tiles, int* status, int tiled,
                            cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
   if (E > 1024) return QB_ERR_UNSUPPORTED;
+  if (tiled <= 0 || tiled > E) tiled = E;
   if (n_pairs <= 4096) {
     moe_plan_small_kernel<<<1, 1024, 0, stream>>>(idx, n_pairs, E, BM, plan, sorted_pair, tile_expert, tile_row0,
-                                                  max_tiles, status);
+                                                  max_tiles, status, tiled);
     QB_LAUNCH_CHECK();
     return 0;
   }
@@ -624,7 +647,7 @@ extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan
   const int blocks = min((n_pairs + 255) / 256, 1024);
   moe_count_kernel<<<blocks, 256, 0, stream>>>(idx, n_pairs, E, counts, status);
   moe_scan_kernel<<<1, 1024, 0, stream>>>(counts, offsets, num_tiles, plan + 3 * E + 4, tile_expert, tile_row0, E,
-                                          BM, max_tiles);
+                                          BM, max_tiles, tiled);
   moe_scatter_kernel<<<blocks, 256, 0, stream>>>(idx, n_pairs, E, offsets, cursor, sorted_pair);
   QB_LAUNCH_CHECK();
   return 0;
@@ -773,6 +796,31 @@ extern "C" int qb_moe_grouped_simt(int mode, const void* x, int x_dtype, const v
     else
       return QB_ERR_BAD_ARG;
   })));
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Experts without weights that hand their input through: for every (token, slot) pair whose chosen expert is
+// >= first_identity, y[pair, :] = w[pair] * x[token, :] (float32).  The other pairs are the product kernels'.
+// ---------------------------------------------------------------------------------------------
+template <typename X>
+__global__ void identity_slots_kernel(const X* __restrict__ x, const int* __restrict__ idx, const float* __restrict__ w,
+                                      float* __restrict__ y, int n_pairs, int top_k, int H, int first_identity) {
+  const int pair = blockIdx.x;
+  if (pair >= n_pairs || idx[pair] < first_identity) return;
+  const X* xrow = x + (size_t)(pair / top_k) * H;
+  float* yrow = y + (size_t)pair * H;
+  const float wt = w[pair];
+  for (int i = threadIdx.x; i < H; i += blockDim.x) yrow[i] = wt * qb_to_float<X>(xrow[i]);
+}
+
+extern "C" int qb_identity_slots(const void* x, int x_dtype, const int* idx, const float* w, float* y, int n_pairs,
+                                 int top_k, int H, int first_identity, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (top_k <= 0 || H <= 0) return QB_ERR_BAD_ARG;
+  QB_DISPATCH_DTYPE(x_dtype, X, identity_slots_kernel<X><<<n_pairs, 128, 0, stream>>>((const X*)x, idx, w, y, n_pairs,
+                                                                                       top_k, H, first_identity));
   QB_LAUNCH_CHECK();
   return 0;
 }

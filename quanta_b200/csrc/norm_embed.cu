@@ -166,51 +166,69 @@ extern "C" int qb_add_rmsnorm(float* h, const void* delta, int delta_dtype, int 
 }
 
 // ---------------------------------------------------------------------------------------------
-// A sublayer's output y that is RMS-normed (gain g, eps_y) BEFORE it joins the residual stream, fused with
-// the norm that follows: row r (token rows[r] if rows != null, else r):
-//   d = g * (y[tok,:] * rsqrt(mean(y^2) + eps_y));  x = h[tok,:] + d;  if store_h: h[tok,:] = x
-//   out[r,:] = w * (x * rsqrt(mean(x^2) + eps))
-// The same operations as the two kernels it replaces (the norm of y written to memory, then the adding norm);
-// a row's sums are added in a fixed order that depends on H alone.  The row is held in shared memory between
-// the passes.
+// A sublayer's output that is RMS-normed (gain g, eps_y) BEFORE it joins the residual stream, fused with
+// what follows.  The output may still be a sum that nobody has taken:
+//   z = y_scale * (sum_s y[tok, s, :] + y_bias) + x2_scale * (y2[tok, :] + y2_bias)      (slots in order; y2 and
+//                                                                                        the biases may be null)
+// Row r (token rows[r] if rows != null, else r):
+//   d = g * (z * rsqrt(mean(z^2) + eps_y));  x = h[tok,:] + d;  if store_h: h[tok,:] = x
+//   out[r,:] = w * (x * rsqrt(mean(x^2) + eps))        (w null: out[r,:] = x, the stream itself for a sublayer
+//                                                        that reads it without a norm)
+// y null: nothing joins (d = 0).  A row's sums are added in a fixed order that depends on H alone.  The row is
+// held in shared memory between the passes.
 // ---------------------------------------------------------------------------------------------
 template <typename O>
-__global__ void normed_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ y,
-                                          const float* __restrict__ g, float eps_y, const float* __restrict__ w,
-                                          O* __restrict__ out, const int* __restrict__ rows, int n_rows, int H,
-                                          float eps, int store_h) {
+__global__ void normed_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ y, int S, float y_scale,
+                                          const float* __restrict__ y_bias, const float* __restrict__ y2,
+                                          float y2_scale, const float* __restrict__ y2_bias,
+                                          const float* __restrict__ g, float eps_y,
+                                          const float* __restrict__ w, O* __restrict__ out,
+                                          const int* __restrict__ rows, int n_rows, int H, float eps, int store_h) {
   extern __shared__ float row_buf[];      // H floats + 32 scratch
   float* scratch = row_buf + H;
   const int r = blockIdx.x;
   if (r >= n_rows) return;
   const int tok = rows ? rows[r] : r;
   float* hrow = h + (size_t)tok * H;
-  const float* yrow = y + (size_t)tok * H;
+  const float* yrow = y ? y + (size_t)tok * S * H : nullptr;
+  const float* y2row = y2 ? y2 + (size_t)tok * H : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = yrow[i];
+  for (int i = threadIdx.x; yrow != nullptr && i < H; i += blockDim.x) {
+    float v = yrow[i];
+    for (int s = 1; s < S; ++s) v += yrow[(size_t)s * H + i];
+    if (y_bias) v += y_bias[i];
+    v *= y_scale;
+    if (y2row) v = fmaf(y2_scale, y2row[i] + (y2_bias ? y2_bias[i] : 0.f), v);
     row_buf[i] = v;
     ss += v * v;
   }
   const float y_inv = rsqrtf(qb_block_sum(ss, scratch) / (float)H + eps_y);
   ss = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float x = hrow[i] + g[i] * (row_buf[i] * y_inv);
+    const float x = yrow != nullptr ? hrow[i] + g[i] * (row_buf[i] * y_inv) : hrow[i];
     row_buf[i] = x;
-    if (store_h) hrow[i] = x;
+    if (store_h && yrow != nullptr) hrow[i] = x;
     ss += x * x;
   }
-  const float total = qb_block_sum(ss, scratch);
   if (out == nullptr) return;
-  const float r_inv = rsqrtf(total / (float)H + eps);
   O* orow = out + (size_t)r * H;
+  if (w == nullptr) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = qb_from_float<O>(row_buf[i]);
+    return;
+  }
+  const float total = qb_block_sum(ss, scratch);
+  const float r_inv = rsqrtf(total / (float)H + eps);
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = qb_from_float<O>(w[i] * (row_buf[i] * r_inv));
 }
 
-extern "C" int qb_normed_add_rmsnorm(float* h, const float* y, const float* g, float eps_y, const float* w, void* out,
+extern "C" int qb_normed_add_rmsnorm(float* h, const float* y, int S, float y_scale, const float* y_bias,
+                                     const float* y2, float y2_scale, const float* y2_bias, const float* g,
+                                     float eps_y, const float* w, void* out,
                                      int out_dtype, const int* rows, int n_rows, int H, float eps, int store_h,
                                      cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (S < 1 || (y != nullptr && g == nullptr)) return QB_ERR_BAD_ARG;
   const size_t smem = (size_t)(H + 32) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
   const int threads = H >= 2048 ? 512 : 256;
@@ -220,7 +238,8 @@ extern "C" int qb_normed_add_rmsnorm(float* h, const float* y, const float* g, f
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
-    kern<<<n_rows, threads, smem, stream>>>(h, y, g, eps_y, w, (O*)out, rows, n_rows, H, eps, store_h);
+    kern<<<n_rows, threads, smem, stream>>>(h, y, S, y_scale, y_bias, y2, y2_scale, y2_bias, g, eps_y, w,
+                                            (O*)out, rows, n_rows, H, eps, store_h);
   });
   QB_LAUNCH_CHECK();
   return 0;

@@ -9,8 +9,12 @@
 //            pair_axis[j] and angle float(pos) * inv_freq[j]  (src/quanta/minimax/model_m3.py:83-96)
 //   q     <- q * (1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1))     (temp_every > 0: a query
 //            temperature that grows with the position, float32)
+//   v     <- (1 - lambda) v + lambda v_first      (v_first: float32 values [T, nkv * vd] that an earlier layer left for
+//            the same tokens, lambda one number on the device; v_export: this layer leaves its own values there)
 //   q     -> q_out [T, nq, hd];  k -> pages [page, kv_head, slot, hd], v -> pages [page, kv_head, slot, vd]
 //            through the block table (keys and values may have different head sizes)
+// The rows may be float32 accumulators of the projection while q and the cache are in the activation dtype, and a
+// bias (float32, laid out like the row's [q | k | v]) may be added first.  A per-head norm may have no gains.
 // One rounding to the activation dtype, at the store.  One block per token.
 #include "common.cuh"
 
@@ -18,15 +22,16 @@
 #define NORM_PER_LAYER 1
 #define NORM_PER_HEAD 2
 
-template <typename A>
+template <typename IN, typename A>
 __global__ void qknorm_rope_write_kernel(
-    const A* __restrict__ qkv, int row_stride, A* __restrict__ q_out, A* __restrict__ k_cache, A* __restrict__ v_cache,
+    const IN* __restrict__ qkv, int row_stride, A* __restrict__ q_out, A* __restrict__ k_cache, A* __restrict__ v_cache,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, int norm_kind, float eps,
     const float* __restrict__ inv_freq, const int* __restrict__ pair_axis,
     const int* __restrict__ positions, int n_axes, const int* __restrict__ tok_pos,
     const int* __restrict__ tok_req, const int* __restrict__ block_table, int bt_stride, int T, int nq,
     int nkv_all, int hd, int vd, int has_kv, int rd, float temp_coef, int temp_every, int page_size, int num_pages,
-    int vec, int* status) {
+    int vec, const float* __restrict__ bias, const float* __restrict__ v_first, const float* __restrict__ v_lambda,
+    float* __restrict__ v_export, int* status) {
   extern __shared__ float smem[];
   const int t = blockIdx.x;
   if (t >= T) return;
@@ -36,7 +41,7 @@ __global__ void qknorm_rope_write_kernel(
   float* cs = buf + qn + kn;         // [rd/2] cos, [rd/2] sin
   float* scratch = cs + rd;          // 32 + (nq + nkv) head statistics
   float* head_r = scratch + 32;
-  const A* row = qkv + (size_t)t * row_stride;
+  const IN* row = qkv + (size_t)t * row_stride;
   const int half = rd / 2;
   // Where this token's K and V go is a chain of three dependent loads (position, request, page id), and the
   // norm gains come from memory that the layer's expert weights have pushed out of L2: both are asked for
@@ -56,11 +61,18 @@ __global__ void qknorm_rope_write_kernel(
 #pragma unroll 4
     for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
       float v[8];
-      QbVec8<A>::load(row + c * 8, v);
+      QbVec8<IN>::load(row + c * 8, v);
+      if (bias != nullptr) {
+        float b[8];
+        QbVec8<float>::load(bias + c * 8, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += b[e];
+      }
       QbVec8<float>::store(buf + c * 8, v);
     }
   } else {
-    for (int i = threadIdx.x; i < qn + kn; i += blockDim.x) buf[i] = qb_to_float<A>(row[i]);
+    for (int i = threadIdx.x; i < qn + kn; i += blockDim.x)
+      buf[i] = qb_to_float<IN>(row[i]) + (bias != nullptr ? bias[i] : 0.f);
   }
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     const int ax = pair_axis ? pair_axis[j] : 0;
@@ -119,7 +131,7 @@ __global__ void qknorm_rope_write_kernel(
     __syncthreads();
     for (int i = threadIdx.x; i < qn + kn; i += blockDim.x) {
       const int h = i / hd, d = i % hd;
-      const float w = h < nq ? q_norm_w[d] : k_norm_w[d];
+      const float w = q_norm_w == nullptr ? 1.f : h < nq ? q_norm_w[d] : k_norm_w[d];
       buf[i] = w * (buf[i] * head_r[h]);
     }
     __syncthreads();
@@ -155,7 +167,11 @@ __global__ void qknorm_rope_write_kernel(
     return;
   }
   const int slot = pos % page_size;
-  const A* vrow = row + qn + kn;
+  const IN* vrow = row + qn + kn;
+  const float* vbias = bias != nullptr ? bias + qn + kn : nullptr;
+  const float lam = v_first != nullptr ? v_lambda[0] : 0.f;
+  const float* vf = v_first != nullptr ? v_first + (size_t)t * vn : nullptr;
+  float* vx = v_export != nullptr ? v_export + (size_t)t * vn : nullptr;
   if (vec) {
     for (int c = threadIdx.x; c < kn / 8; c += blockDim.x) {
       const int i = c * 8, h = i / hd, d = i % hd;
@@ -166,26 +182,49 @@ __global__ void qknorm_rope_write_kernel(
     for (int c = threadIdx.x; c < vn / 8; c += blockDim.x) {
       const int i = c * 8, h = i / vd, d = i % vd;
       float vv[8];
-      QbVec8<A>::load(vrow + i, vv);
-      QbVec8<A>::store(v_cache + (((size_t)page * nkv + h) * page_size + slot) * vd + d, vv);   // V passes through unchanged
+      QbVec8<IN>::load(vrow + i, vv);
+      if (vbias != nullptr) {
+        float b[8];
+        QbVec8<float>::load(vbias + i, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vv[e] += b[e];
+      }
+      if (vx != nullptr) QbVec8<float>::store(vx + i, vv);
+      if (vf != nullptr) {
+        float f[8];
+        QbVec8<float>::load(vf + i, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vv[e] = (1.f - lam) * vv[e] + lam * f[e];
+      }
+      QbVec8<A>::store(v_cache + (((size_t)page * nkv + h) * page_size + slot) * vd + d, vv);
     }
   } else {
     for (int i = threadIdx.x; i < kn; i += blockDim.x)
       k_cache[(((size_t)page * nkv + i / hd) * page_size + slot) * hd + i % hd] = qb_from_float<A>(buf[qn + i]);
-    for (int i = threadIdx.x; i < vn; i += blockDim.x)
-      v_cache[(((size_t)page * nkv + i / vd) * page_size + slot) * vd + i % vd] = vrow[i];
+    for (int i = threadIdx.x; i < vn; i += blockDim.x) {
+      float v = qb_to_float<IN>(vrow[i]) + (vbias != nullptr ? vbias[i] : 0.f);
+      if (vx != nullptr) vx[i] = v;
+      if (vf != nullptr) v = (1.f - lam) * v + lam * vf[i];
+      v_cache[(((size_t)page * nkv + i / vd) * page_size + slot) * vd + i % vd] = qb_from_float<A>(v);
+    }
   }
 }
 
 extern "C" int qb_qknorm_rope_write(
-    const void* qkv, int dtype, int row_stride, void* q_out, void* k_cache, void* v_cache, const float* q_norm_w,
+    const void* qkv, int in_dtype, int dtype, int row_stride, void* q_out, void* k_cache, void* v_cache, const float* q_norm_w,
     const float* k_norm_w, int norm_kind, float eps, const float* inv_freq, const int* pair_axis,
     const int* positions, int n_axes, const int* tok_pos, const int* tok_req, const int* block_table,
     int bt_stride, int T, int nq, int nkv, int hd, int vd, int has_kv, int rd, float temp_coef, int temp_every,
-    int page_size, int num_pages, int* status, cudaStream_t stream) {
+    int page_size, int num_pages, const float* bias, const float* v_first, const float* v_lambda, float* v_export,
+    int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rd % 2 || rd > hd || rd < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || hd <= 0 || vd <= 0) return QB_ERR_BAD_ARG;
-  if (norm_kind != NORM_NONE && (q_norm_w == nullptr || (has_kv && k_norm_w == nullptr))) return QB_ERR_BAD_ARG;
+  // a norm over the whole row needs gains; a per-head norm may have none (both null)
+  if (norm_kind == NORM_PER_LAYER && (q_norm_w == nullptr || (has_kv && k_norm_w == nullptr))) return QB_ERR_BAD_ARG;
+  if (norm_kind == NORM_PER_HEAD && q_norm_w != nullptr && has_kv && k_norm_w == nullptr) return QB_ERR_BAD_ARG;
+  if (norm_kind == NORM_PER_HEAD && q_norm_w == nullptr && k_norm_w != nullptr) return QB_ERR_BAD_ARG;
+  if ((v_first != nullptr && v_lambda == nullptr) || ((v_first != nullptr || v_export != nullptr) && !has_kv)) return QB_ERR_BAD_ARG;
+  if (in_dtype != dtype && in_dtype != QB_F32) return QB_ERR_BAD_ARG;
   if (!has_kv && k_cache != nullptr) return QB_ERR_BAD_ARG;
   const int nk = has_kv ? nkv : 0;
   if (row_stride < nq * hd + nk * (hd + vd)) return QB_ERR_BAD_ARG;
@@ -193,19 +232,26 @@ extern "C" int qb_qknorm_rope_write(
   const int vec = (hd % 8 == 0 && vd % 8 == 0 && row_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0) ? 1 : 0;
   const size_t smem = (size_t)((nq + nk) * hd + rd + 32 + nq + nk) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
-  QB_DISPATCH_DTYPE(dtype, A, {
-    auto kern = qknorm_rope_write_kernel<A>;
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    // steps of few tokens: more threads a token, so that each of the kernel's phases is short
-    const int threads = T <= 64 ? 1024 : 256;
-    kern<<<T, threads, smem, stream>>>((const A*)qkv, row_stride, (A*)q_out, (A*)k_cache, (A*)v_cache, q_norm_w,
-                                       k_norm_w, norm_kind, eps, inv_freq, pair_axis, positions, n_axes, tok_pos,
-                                       tok_req, block_table, bt_stride, T, nq, nkv, hd, vd, has_kv, rd, temp_coef,
-                                       temp_every, page_size, num_pages, vec, status);
-  });
+#define QB_ROPE_LAUNCH(IN, A)                                                                                   \
+  do {                                                                                                          \
+    auto kern = qknorm_rope_write_kernel<IN, A>;                                                                \
+    if (smem > 48 * 1024) {                                                                                     \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+      if (e != cudaSuccess) return (int)e;                                                                      \
+    }                                                                                                           \
+    kern<<<T, threads, smem, stream>>>((const IN*)qkv, row_stride, (A*)q_out, (A*)k_cache, (A*)v_cache, q_norm_w, \
+                                       k_norm_w, norm_kind, eps, inv_freq, pair_axis, positions, n_axes, tok_pos, \
+                                       tok_req, block_table, bt_stride, T, nq, nkv, hd, vd, has_kv, rd, temp_coef, \
+                                       temp_every, page_size, num_pages, vec, bias, v_first, v_lambda, v_export,  \
+                                       status);                                                                 \
+  } while (0)
+  // steps of few tokens: more threads a token, so that each of the kernel's phases is short
+  const int threads = T <= 64 ? 1024 : 256;
+  if (dtype == QB_F32) QB_ROPE_LAUNCH(float, float);
+  else if (dtype == QB_BF16 && in_dtype == QB_F32) QB_ROPE_LAUNCH(float, __nv_bfloat16);
+  else if (dtype == QB_BF16) QB_ROPE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return QB_ERR_BAD_ARG;
+#undef QB_ROPE_LAUNCH
   QB_LAUNCH_CHECK();
   return 0;
 }

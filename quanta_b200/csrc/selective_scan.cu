@@ -1,0 +1,122 @@
+// Selective state-space scan: a linear recurrence per channel whose decay and input depend on the token.
+//
+// Per channel c (of `inner`) and state index n (of N), with u the channel's input, dt its step size, B and C the
+// token's input and output vectors (shared by all channels), A = -exp(A_log) and D per channel:
+//   dt[t, c] = softplus(sum_r W_dt[c, r] * low[t, r] + dt_bias[c])                 (low: R numbers a token)
+//   S[c, n] <- exp(dt[t, c] * A[c, n]) * S[c, n] + dt[t, c] * u[t, c] * B[t, n]
+//   y[t, c]  = sum_n S[c, n] * C[t, n] + D[c] * u[t, c]
+//   out[t, c] = y[t, c] * silu(z[t, c])
+// S is float32, one [inner, N] matrix per request in its state slot, zero at admission.  Step sizes, decays,
+// exponentials, the state and the gate are float32; u is read in the activation dtype (it is the rounded output
+// of the convolution that also feeds the projection of low, B and C), `proj` holds that projection's float32
+// accumulators [low | B | C] and z comes from the float32 rows of the input projection.
+//
+// Two launches: the step sizes of all tokens at once, then the chain in time: eight lanes own a channel (each a
+// stride-8 share of its N states, in registers), a block owns 16 channels of one request and walks the request's
+// rows of this step in order.  Single tokens and portions are the same code and a channel's arithmetic does not
+// depend on which block owns it, so cut and batch change nothing.
+#include "common.cuh"
+
+constexpr int SS_LANES = 8;            // lanes that share a channel
+constexpr int SS_CH = 16;              // channels a block
+constexpr int SS_MAX_STATE = 256;
+
+__device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// dt[t, c] for all tokens: a thread a (token, channel)
+__global__ void scan_steps_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ w_dt,
+                                  const float* __restrict__ dt_bias, float* __restrict__ dt, int T, int inner, int R) {
+  const size_t n = (size_t)T * inner;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / inner), c = (int)(i % inner);
+    const float* low = proj + (size_t)t * proj_stride;
+    const float* w = w_dt + (size_t)c * R;
+    float acc = 0.f;
+    for (int r = 0; r < R; ++r) acc = fmaf(w[r], low[r], acc);
+    dt[i] = ss_softplus(acc + dt_bias[c]);
+  }
+}
+
+// NPL: states a lane holds, N <= 8 * NPL
+template <typename U, typename O, int NPL>
+__global__ void __launch_bounds__(SS_CH * SS_LANES)
+scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const float* __restrict__ proj,
+                  int proj_stride, int b_off, int c_off, const float* __restrict__ z, int z_stride,
+                  const float* __restrict__ A, const float* __restrict__ D, float* __restrict__ state,
+                  O* __restrict__ out, const int* __restrict__ req_start, const int* __restrict__ req_slot, int inner,
+                  int N) {
+  const int r = blockIdx.y;
+  const int first = req_start[r], last = req_start[r + 1];
+  if (last <= first) return;
+  const int sub = threadIdx.x % SS_LANES;
+  const int c = blockIdx.x * SS_CH + threadIdx.x / SS_LANES;
+  const bool live = c < inner;
+  const int cc = live ? c : inner - 1;                       // idle lanes walk along (the shuffles want whole groups)
+  float* Srow = state + ((size_t)req_slot[r] * inner + cc) * N;
+  float S[NPL], a[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int n = sub + SS_LANES * i;
+    S[i] = n < N ? Srow[n] : 0.f;
+    a[i] = n < N ? A[(size_t)cc * N + n] : 0.f;
+  }
+  const float d_c = D[cc];
+  for (int t = first; t < last; ++t) {
+    const float dtv = dt[(size_t)t * inner + cc];
+    const float uv = qb_to_float<U>(u[(size_t)t * inner + cc]);
+    const float* Bt = proj + (size_t)t * proj_stride + b_off;
+    const float* Ct = proj + (size_t)t * proj_stride + c_off;
+    const float du = dtv * uv;
+    float y = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = sub + SS_LANES * i;
+      if (n < N) {
+        S[i] = fmaf(expf(dtv * a[i]), S[i], du * Bt[n]);
+        y = fmaf(S[i], Ct[n], y);
+      }
+    }
+#pragma unroll
+    for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+    if (sub == 0 && live) {
+      y = fmaf(d_c, uv, y);
+      const float zv = z[(size_t)t * z_stride + c];
+      out[(size_t)t * inner + c] = qb_from_float<O>(y * (zv / (1.f + expf(-zv))));
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = sub + SS_LANES * i;
+      if (n < N) Srow[n] = S[i];
+    }
+  }
+}
+
+// u [T, inner] in the activation dtype; proj float32 rows [low (R) | B (N) | C (N) | ...]; z float32 rows of
+// z_stride; w_dt float32 [inner, R]; A float32 [inner, N] (already -exp(A_log)); state float32 [slots, inner, N];
+// dt float32 scratch [T, inner]; out [T, inner] in the activation dtype.
+extern "C" int qb_selective_scan(const void* u, int dtype, const float* proj, int proj_stride, const float* z,
+                                 int z_stride, const float* w_dt, const float* dt_bias, const float* A, const float* D,
+                                 float* state, float* dt, void* out, const int* req_start, const int* req_slot, int T,
+                                 int R_req, int inner, int N, int rank, cudaStream_t stream) {
+  if (T <= 0 || R_req <= 0) return 0;
+  if (inner <= 0 || N <= 0 || rank <= 0 || proj_stride < rank + 2 * N || z_stride < inner) return QB_ERR_BAD_ARG;
+  if (N > SS_MAX_STATE || R_req > 65535) return QB_ERR_UNSUPPORTED;
+  const size_t n = (size_t)T * inner;
+  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+  scan_steps_kernel<<<blocks, 256, 0, stream>>>(proj, proj_stride, w_dt, dt_bias, dt, T, inner, rank);
+  QB_LAUNCH_CHECK();
+  dim3 grid((inner + SS_CH - 1) / SS_CH, R_req);
+#define QB_SS_LAUNCH(NPL)                                                                                             \
+  QB_DISPATCH_DTYPE(dtype, U, (scan_chain_kernel<U, U, NPL><<<grid, SS_CH * SS_LANES, 0, stream>>>(                   \
+      (const U*)u, dt, proj, proj_stride, rank, rank + N, z, z_stride, A, D, state, (U*)out, req_start, req_slot, inner, N)))
+  if (N <= 8 * 2) QB_SS_LAUNCH(2);
+  else if (N <= 8 * 4) QB_SS_LAUNCH(4);
+  else if (N <= 8 * 8) QB_SS_LAUNCH(8);
+  else if (N <= 8 * 16) QB_SS_LAUNCH(16);
+  else QB_SS_LAUNCH(32);
+#undef QB_SS_LAUNCH
+  QB_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,6 +1,9 @@
-// Short causal convolution over time on every channel, with the input added back, and its state.
+// Short causal convolution over time on every channel, and its state.  Two forms:
 //
-//   y_t = x_t + sum_{j < taps} w[:, j] * x_{t - taps + 1 + j}          (zeros before a sequence's start)
+//   y_t = x_t + sum_{j < taps} w[:, j] * x_{t - taps + 1 + j}          (act 0: the input added back)
+//   y_t = silu(b + sum_{j < taps} w[:, j] * x_{t - taps + 1 + j})      (act 1: a bias and silu, nothing added back)
+//
+// with zeros before a sequence's start.  The rows of x may be a column range of wider rows (x_stride).
 //
 // x are the step's rows (float32, e.g. the output of a norm), all requests one after the other; the
 // taps-1 rows that precede a request's first row of this step come from the request's state slot,
@@ -17,7 +20,8 @@ template <typename O>
 __global__ void short_conv_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                        const float* __restrict__ state, O* __restrict__ out,
                                        const int* __restrict__ tok_req, const int* __restrict__ req_start,
-                                       const int* __restrict__ req_slot, int T, int C, int taps) {
+                                       const int* __restrict__ req_slot, int T, int C, int taps, int x_stride,
+                                       const float* __restrict__ bias, int act) {
   const int t = blockIdx.x;
   if (t >= T) return;
   const int r = tok_req[t];
@@ -25,23 +29,28 @@ __global__ void short_conv_rows_kernel(const float* __restrict__ x, const float*
   const int hist = taps - 1;
   const float* st = state + (size_t)req_slot[r] * hist * C;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const float cur = x[(size_t)t * C + c];
+    const float cur = x[(size_t)t * x_stride + c];
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {
       const int back = hist - j;          // how many rows before t
       float v;
       if (back == 0) v = cur;
-      else if (t - back >= first) v = x[(size_t)(t - back) * C + c];
+      else if (t - back >= first) v = x[(size_t)(t - back) * x_stride + c];
       else v = st[(size_t)(hist - (first - (t - back))) * C + c];   // state row hist-1 is the newest
       acc += w[(size_t)c * taps + j] * v;
     }
-    out[(size_t)t * C + c] = qb_from_float<O>(cur + acc);
+    if (act == 1) {
+      acc += bias != nullptr ? bias[c] : 0.f;
+      out[(size_t)t * C + c] = qb_from_float<O>(acc / (1.f + expf(-acc)));
+    } else {
+      out[(size_t)t * C + c] = qb_from_float<O>(cur + acc);
+    }
   }
 }
 
 __global__ void short_conv_state_kernel(const float* __restrict__ x, float* __restrict__ state,
                                         const int* __restrict__ req_start, const int* __restrict__ req_slot,
-                                        int R, int C, int taps) {
+                                        int R, int C, int taps, int x_stride) {
   const int r = blockIdx.x;
   if (r >= R) return;
   const int first = req_start[r], n = req_start[r + 1] - first;
@@ -53,22 +62,22 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, float* __re
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     for (int i = 0; i < hist; ++i) {
       const int src = n - hist + i;
-      st[(size_t)i * C + c] = src >= 0 ? x[(size_t)(first + src) * C + c] : st[(size_t)(i + n) * C + c];
+      st[(size_t)i * C + c] = src >= 0 ? x[(size_t)(first + src) * x_stride + c] : st[(size_t)(i + n) * C + c];
     }
   }
 }
 
 extern "C" int qb_short_conv(const float* x, const float* w, float* state, void* out, int out_dtype,
                              const int* tok_req, const int* req_start, const int* req_slot, int T, int R,
-                             int C, int taps, cudaStream_t stream) {
+                             int C, int taps, int x_stride, const float* bias, int act, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (taps < 1 || C <= 0) return QB_ERR_BAD_ARG;
+  if (taps < 1 || C <= 0 || x_stride < C || (act != 0 && act != 1)) return QB_ERR_BAD_ARG;
   const int threads = C >= 1024 ? 256 : 128;
   QB_DISPATCH_DTYPE(out_dtype, O, short_conv_rows_kernel<O><<<T, threads, 0, stream>>>(
-      x, w, state, (O*)out, tok_req, req_start, req_slot, T, C, taps));
+      x, w, state, (O*)out, tok_req, req_start, req_slot, T, C, taps, x_stride, bias, act));
   QB_LAUNCH_CHECK();
   if (taps > 1) {
-    short_conv_state_kernel<<<R, threads, 0, stream>>>(x, state, req_start, req_slot, R, C, taps);
+    short_conv_state_kernel<<<R, threads, 0, stream>>>(x, state, req_start, req_slot, R, C, taps, x_stride);
     QB_LAUNCH_CHECK();
   }
   return 0;

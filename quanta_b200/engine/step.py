@@ -76,10 +76,20 @@ class Engine:
         self.manager = CacheManager(needs, page_size, num_pages, max_requests)
         # per cache-writing schedule position: the pages of every stream its mixer declared
         self.kv: dict[int, dict[str, torch.Tensor]] = {}
-        for pos, spec in enumerate(needs):
-            if spec is not None:
-                self.kv[pos] = {st.name: torch.zeros((num_pages, st.heads, page_size, st.width), dtype=model.dtype,
-                                                     device=self.device) for st in spec.streams}
+        self.stream_group: dict[int, dict[str, int]] = {}     # schedule position -> stream name -> its page group
+        for pos, need in enumerate(needs):
+            if need is None:
+                continue
+            self.kv[pos], self.stream_group[pos] = {}, {}
+            specs = need if isinstance(need, (tuple, list)) else (need,)
+            for spec, g in zip(specs, self.manager.groups_of[pos]):
+                pages = self.manager.groups[g].pool.num_pages
+                for st in spec.streams:
+                    if st.name in self.kv[pos]:
+                        raise ValueError(f"schedule position {pos}: two cache streams are named {st.name!r}")
+                    self.kv[pos][st.name] = torch.zeros((pages, st.heads, page_size, st.width), dtype=model.dtype,
+                                                        device=self.device)
+                    self.stream_group[pos][st.name] = g
         self.state: list[dict[str, torch.Tensor]] = []
         for need in model.state_needs():
             self.state.append({name: torch.zeros((max_requests, *shape), dtype=dt, device=self.device)
@@ -250,7 +260,8 @@ class Engine:
             if src in self.kv:
                 caches.append(LayerCache(streams=self.kv[src], page_size=self.page_size,
                                          block_table=d_tables[self.manager.group_of[src]],
-                                         write=entry.read_cache_of is None))
+                                         write=entry.read_cache_of is None,
+                                         tables={n: d_tables[g] for n, g in self.stream_group[src].items()}))
             else:
                 caches.append(None)
         return d_ids, d_want, ctx, caches

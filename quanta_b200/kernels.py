@@ -208,24 +208,44 @@ def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
                                 ctypes.c_float(eps), int(store_h), _stream()), "add_rmsnorm")
 
 
-def normed_add_rmsnorm(h: torch.Tensor, y: torch.Tensor, y_gain: torch.Tensor, y_eps: float, weight: torch.Tensor,
-                       eps: float, out: torch.Tensor | None, rows: torch.Tensor | None = None, store_h: bool = True) -> None:
-    """``h += y_gain * y * rsqrt(mean(y^2) + y_eps)`` (float32) and ``out = weight * h * rsqrt(mean(h^2) + eps)``: a
+def normed_add_rmsnorm(h: torch.Tensor, y: torch.Tensor | None, y_gain: torch.Tensor | None, y_eps: float,
+                       weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
+                       rows: torch.Tensor | None = None, store_h: bool = True, *, y_scale: float = 1.0,
+                       y_bias: torch.Tensor | None = None, extra: torch.Tensor | None = None, extra_scale: float = 1.0,
+                       extra_bias: torch.Tensor | None = None) -> None:
+    """``h += y_gain * z * rsqrt(mean(z^2) + y_eps)`` (float32) and ``out = weight * h * rsqrt(mean(h^2) + eps)``: a
     sublayer's output that is normed before it joins the stream, and the norm that follows, in one launch.
-    ``y`` float32 ``[T, H]``; ``rows`` / ``store_h`` / ``out`` None as in ``add_rmsnorm``."""
-    for t, n in ((h, "h"), (y, "y"), (y_gain, "y_gain")):
-        _want(t, torch.float32, n)
+    ``z = y_scale * (sum_s y[:, s] + y_bias) + extra_scale * (extra + extra_bias)``: ``y`` float32 ``[T, H]`` or
+    ``[T, S, H]`` (slots added in order), ``extra`` float32 ``[T, H]`` or None, the biases ``[H]`` or None.
+    ``weight`` None with ``out``: ``out`` is the stream itself (for a sublayer that reads it without a norm);
+    ``y`` None: nothing joins.  ``rows`` / ``store_h`` / ``out`` None as in ``add_rmsnorm``."""
+    _want(h, torch.float32, "h")
     T, H = h.shape
-    if tuple(y.shape) != (T, H) or y_gain.numel() != H:
-        raise ValueError("normed_add_rmsnorm: shape mismatch")
+    S = 1
+    if y is not None:
+        _want(y, torch.float32, "y"); _want(y_gain, torch.float32, "y_gain")
+        S = y.shape[1] if y.dim() == 3 else 1
+        if y.shape[0] != T or y.shape[-1] != H or y_gain.numel() != H:
+            raise ValueError("normed_add_rmsnorm: shape mismatch")
+    elif extra is not None:
+        raise ValueError("normed_add_rmsnorm: a second addend without a first")
+    for t, n in ((y_bias, "y_bias"), (extra, "extra"), (extra_bias, "extra_bias")):
+        if t is not None:
+            _want(t, torch.float32, n)
+            if t.shape[-1] != H or t.numel() != (T * H if n == "extra" else H):
+                raise ValueError(f"normed_add_rmsnorm: {n} shape mismatch")
     n = T if rows is None else rows.numel()
     if rows is not None:
         _want(rows, torch.int32, "rows")
     if out is not None:
-        _want(weight, torch.float32, "weight")
-        if out.shape[0] != n or out.shape[1] != H or weight.numel() != H:
-            raise ValueError("normed_add_rmsnorm: out or weight shape mismatch")
-    _check(lib().qb_normed_add_rmsnorm(_p(h), _p(y), _p(y_gain), ctypes.c_float(y_eps),
+        if out.shape[0] != n or out.shape[1] != H:
+            raise ValueError("normed_add_rmsnorm: out shape mismatch")
+        if weight is not None:
+            _want(weight, torch.float32, "weight")
+            if weight.numel() != H:
+                raise ValueError("normed_add_rmsnorm: weight shape mismatch")
+    _check(lib().qb_normed_add_rmsnorm(_p(h), _p(y), S, ctypes.c_float(y_scale), _p(y_bias), _p(extra),
+                                       ctypes.c_float(extra_scale), _p(extra_bias), _p(y_gain), ctypes.c_float(y_eps),
                                        _p(weight) if out is not None else ctypes.c_void_p(0), _p(out),
                                        _code(out) if out is not None else F32, _p(rows), n, H, ctypes.c_float(eps),
                                        int(store_h), _stream()), "normed_add_rmsnorm")
@@ -252,28 +272,40 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kind: int, eps: float,
                       inv_freq, pair_axis, positions, tok_pos, tok_req, block_table, nq: int, nkv: int,
                       hd: int, rd: int, page_size: int, status, *, vd: int | None = None, has_kv: bool = True,
-                      q_temp_coef: float = 0.0, q_temp_every: int = 0) -> None:
+                      q_temp_coef: float = 0.0, q_temp_every: int = 0, bias=None, v_first=None, v_lambda=None,
+                      v_export=None) -> None:
     """Rows ``[q | k | v | ...]`` of a fused projection (``qkv`` may be wider than the three; its row stride is
     honoured) -> normed, rotated queries in ``q_out`` and keys / values in the pages.  ``vd``: the values' head
     size when it differs from ``hd``; ``has_kv`` False: the rows start with q alone (a layer that reads another
     layer's cache); ``q_temp_every`` > 0: q is multiplied by ``1 + q_temp_coef * ln(floor((pos + 1) /
-    q_temp_every) + 1)``."""
+    q_temp_every) + 1)``.  ``qkv`` may hold the projection's float32 accumulators while ``q_out`` and the cache are
+    bfloat16.  ``bias``: float32, added to the row's ``[q | k | v]`` first.  A per-head norm may come without gains
+    (both None).  ``v_first`` (float32 ``[T, nkv * vd]``) with ``v_lambda`` (one float32 on the device): the values
+    become ``(1 - lambda) v + lambda v_first`` before they are cached; ``v_export``: this layer's own values (bias
+    added, not blended) are left there as float32."""
     T = qkv.shape[0]
     vd = hd if vd is None else int(vd)
     if qkv.stride(1) != 1 or qkv.shape[1] < nq * hd + (nkv * (hd + vd) if has_kv else 0):
         raise ValueError("qknorm_rope_write: qkv width mismatch")
-    if q_out.dtype != qkv.dtype or q_out.numel() != T * nq * hd:
+    if (q_out.dtype != qkv.dtype and qkv.dtype != torch.float32) or q_out.numel() != T * nq * hd:
         raise ValueError("qknorm_rope_write: q_out mismatch")
     num_pages = 0
     if k_cache is not None:
         if not has_kv:
             raise ValueError("qknorm_rope_write: rows without keys and values cannot fill a cache")
-        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+        if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
             raise ValueError("qknorm_rope_write: cache dtype differs from activations")
         if (tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd)
                 or k_cache.shape[0] != v_cache.shape[0]):
             raise ValueError("qknorm_rope_write: cache shape mismatch")
         num_pages = k_cache.shape[0]
+    n_row = nq * hd + (nkv * (hd + vd) if has_kv else 0)
+    for t, n, size in ((bias, "bias", n_row), (v_first, "v_first", T * nkv * vd), (v_lambda, "v_lambda", 1),
+                       (v_export, "v_export", T * nkv * vd)):
+        if t is not None:
+            _want(t, torch.float32, n)
+            if t.numel() != size:
+                raise ValueError(f"qknorm_rope_write: {n} holds {t.numel()} numbers, {size} wanted")
     _want(inv_freq, torch.float32, "inv_freq")
     if inv_freq.numel() != rd // 2:
         raise ValueError("qknorm_rope_write: inv_freq length")
@@ -282,16 +314,19 @@ def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kin
         _want(t, torch.int32, n)
     if pair_axis is not None:
         _want(pair_axis, torch.int32, "pair_axis")
-    if norm_kind != NORM_NONE:
+    if norm_kind == NORM_PER_HEAD and q_norm_w is None and k_norm_w is None:
+        pass                                    # every head divided by its root mean square, no gains
+    elif norm_kind != NORM_NONE:
         want = (nq * hd, nkv * hd) if norm_kind == NORM_PER_LAYER else (hd, hd)
         if q_norm_w.numel() != want[0] or (has_kv and k_norm_w.numel() != want[1]):
             raise ValueError("qknorm_rope_write: norm weight length does not fit the norm kind")
     _check(lib().qb_qknorm_rope_write(
-        ctypes.c_void_p(qkv.data_ptr()), _code(qkv), int(qkv.stride(0)), _p(q_out), _p(k_cache), _p(v_cache),
+        ctypes.c_void_p(qkv.data_ptr()), _code(qkv), _code(q_out), int(qkv.stride(0)), _p(q_out), _p(k_cache), _p(v_cache),
         _p(q_norm_w), _p(k_norm_w) if has_kv else ctypes.c_void_p(0), norm_kind,
         ctypes.c_float(eps), _p(inv_freq), _p(pair_axis), _p(positions), n_axes, _p(tok_pos), _p(tok_req),
         _p(block_table), block_table.shape[1], T, nq, nkv, hd, vd, int(has_kv), rd, ctypes.c_float(q_temp_coef),
-        int(q_temp_every), page_size, num_pages, _p(status), _stream()), "qknorm_rope_write")
+        int(q_temp_every), page_size, num_pages, _p(bias), _p(v_first), _p(v_lambda), _p(v_export), _p(status),
+        _stream()), "qknorm_rope_write")
 
 
 def paged_attention_simt(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, scale: float,
@@ -389,14 +424,15 @@ def router_gemm_mma(x: torch.Tensor, pieces: torch.Tensor, logits: torch.Tensor)
     _check(lib().qb_router_gemm_mma(_p(x), _p(pieces), _p(logits), T, E, K, _stream()), "router_gemm_mma")
 
 
-ROUTE_SIGMOID_RAW, ROUTE_SIGMOID_RENORM, ROUTE_SOFTMAX_CHOSEN = 0, 1, 2
+ROUTE_SIGMOID_RAW, ROUTE_SIGMOID_RENORM, ROUTE_SOFTMAX_CHOSEN, ROUTE_SOFTMAX_ALL = 0, 1, 2, 3
 
 
 def router_topk(logits, bias, idx_out, w_out, renorm, scale: float) -> None:
     """``logits`` [T, E], or [P, T, E] partial sums that are added in index order first.  ``renorm``: False / True
     (sigmoid scores as they are / divided by their sum; the bias enters the choice only), or
     ``ROUTE_SOFTMAX_CHOSEN``: the choice is by ``logit + bias`` and the weights are the softmax over the chosen
-    values."""
+    values, or ``ROUTE_SOFTMAX_ALL``: the scores are the softmax over all logits, the choice is by ``score + bias``
+    and the weights are the chosen scores as they are."""
     _want(logits, torch.float32, "logits"); _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out")
     n_partials = 1 if logits.dim() == 2 else logits.shape[0]
     T, E = logits.shape[-2:]
@@ -417,11 +453,12 @@ def router_small_selects(n_tokens: int, n_experts: int, top_k: int) -> bool:
 
 def router_small(x, gate, bias, logits, idx_out=None, w_out=None, renorm: bool = True, scale: float = 1.0, *,
                  counters=None, bm: int = 0, plan=None, sorted_pair=None, tile_expert=None, tile_row0=None,
-                 status=None) -> None:
+                 status=None, tiled_experts: int = 0) -> None:
     """Float32 router logits ``logits[T, E] = x[T, K] @ gate[E, K].T`` on the CUDA cores, every logit one sum in
     an order that depends on K alone.  With ``idx_out`` / ``w_out`` / the plan tensors (and
     ``router_small_selects``): the selection (``router_topk``) and the expert plan (``moe_plan``) in the same
-    launch; ``counters``: ``1 + ceil(T / 8)`` int32 that are zero before the call and are left zero."""
+    launch; ``counters``: ``1 + ceil(T / 8)`` int32 that are zero before the call and are left zero.
+    ``tiled_experts`` > 0: only the first so many experts get tiles in the plan (the others have no weights)."""
     _want(gate, torch.float32, "gate"); _want(logits, torch.float32, "logits")
     T, K = x.shape
     E = gate.shape[0]
@@ -442,8 +479,8 @@ def router_small(x, gate, bias, logits, idx_out=None, w_out=None, renorm: bool =
     _check(lib().qb_router_small(_p(x), _code(x), _p(gate), _p(bias), _p(logits), _p(idx_out), _p(w_out), T, E, K, k,
                                  int(renorm), ctypes.c_float(scale), int(select), _p(counters), int(bm), _p(plan),
                                  _p(sorted_pair), _p(tile_expert), _p(tile_row0),
-                                 tile_expert.numel() if tile_expert is not None else 0, _p(status), _stream()),
-           "router_small")
+                                 tile_expert.numel() if tile_expert is not None else 0, _p(status), int(tiled_experts),
+                                 _stream()), "router_small")
 
 
 MOE_SIMT_BM = 32
@@ -454,23 +491,37 @@ def moe_plan_sizes(n_pairs: int, n_experts: int, bm: int) -> tuple[int, int]:
     return 4 * n_experts + 4, (n_pairs + bm - 1) // bm + min(n_experts, n_pairs)
 
 
-def moe_plan(idx, n_experts: int, bm: int, plan, sorted_pair, tile_expert, tile_row0, status) -> None:
+def moe_plan(idx, n_experts: int, bm: int, plan, sorted_pair, tile_expert, tile_row0, status, tiled_experts: int = 0) -> None:
+    """``tiled_experts`` > 0: only the first so many experts get tiles (the others have no weights; their pairs are
+    still counted and sorted)."""
     n_pairs = idx.numel()
     max_tiles = tile_expert.numel()
     _check(lib().qb_moe_plan(_p(idx), n_pairs, n_experts, bm, _p(plan), _p(sorted_pair), _p(tile_expert),
-                             _p(tile_row0), max_tiles, _p(status), _stream()), "moe_plan", 3)
+                             _p(tile_row0), max_tiles, _p(status), int(tiled_experts), _stream()), "moe_plan", 3)
+
+
+def identity_slots(x, idx, w, y, first_identity: int) -> None:
+    """``y[t, j] = w[t, j] * x[t]`` for every choice ``idx[t, j] >= first_identity`` (experts that hand their input
+    through); the other slots are left alone.  ``y`` float32 ``[T, k, H]``."""
+    _want(idx, torch.int32, "idx"); _want(w, torch.float32, "w"); _want(y, torch.float32, "y")
+    T, k, H = y.shape
+    if tuple(x.shape) != (T, H) or idx.numel() != T * k or w.numel() != T * k:
+        raise ValueError("identity_slots: shape mismatch")
+    _check(lib().qb_identity_slots(_p(x), _code(x), _p(idx), _p(w), _p(y), T * k, k, H, int(first_identity), _stream()),
+           "identity_slots")
 
 
 def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
                      n_experts: int, top_k: int) -> None:
     """mode 1: ``out[p, :I] = silu(x[tok] W13_e[:I]^T) * (x[tok] W13_e[I:]^T)``; mode 2:
     ``out[pair] = w[pair] * (x[p] W2_e^T)``; mode 3: ``out[p] = relu(x[tok] W1_e^T)^2`` (ungated experts);
-    rows p sorted by expert (see ``moe_plan``)."""
+    rows p sorted by expert (see ``moe_plan``).  ``weights`` may hold fewer experts than the plan counts when the
+    plan gives the others no tiles."""
     K = x.shape[1]
     N = out.shape[1]
-    want = (n_experts, 2 * N, K) if mode == 1 else (n_experts, N, K)
-    if tuple(weights.shape) != want:
-        raise ValueError(f"moe_grouped: weights {tuple(weights.shape)} != {want}")
+    want = (2 * N, K) if mode == 1 else (N, K)
+    if tuple(weights.shape[1:]) != want or not 0 < weights.shape[0] <= n_experts:
+        raise ValueError(f"moe_grouped: weights {tuple(weights.shape)} do not fit {n_experts} experts of {want}")
     _check(lib().qb_moe_grouped_simt(mode, _p(x), _code(x), _p(weights), _code(weights), _p(out), _code(out),
                                      _p(sorted_pair), _p(pair_w), _p(plan), _p(tile_expert), _p(tile_row0),
                                      tile_expert.numel(), n_experts, top_k, K, N, _stream()), "moe_grouped_simt")
@@ -508,17 +559,19 @@ def gather_rows(x, out, sorted_pair, top_k: int) -> None:
 
 
 def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
-                   n_experts: int, tile_rows: int, status, gather_top_k: int = 0) -> None:
+                   n_experts: int, tile_rows: int, status, gather_top_k: int = 0, weight_experts: int = 0) -> None:
     """Expert products on tcgen05/TMEM fed by TMA.  ``x_rows`` bf16 [pairs, K] in expert order; mode 1:
     ``out[p, :I] = silu(gate) * up`` (bf16), mode 2: ``out[pair(p)] = w[pair(p)] * down`` (float32), mode 3:
     ``out[p] = relu(up)^2`` (bf16; ungated experts, weights ``[E, I, K]``).  The plan's
     tile list must have been made with ``bm = tile_rows``.  Mode 1 or 3 with ``gather_top_k`` > 0: ``x_rows`` is the
     step's activations [T, K] and the kernel fetches the row of token ``pair // gather_top_k`` itself, one
-    TMA box a row (for steps of few tokens: it saves the gathered copy and its launch)."""
+    TMA box a row (for steps of few tokens: it saves the gathered copy and its launch).  ``weight_experts`` > 0: the
+    plan counts ``n_experts`` experts of which only the first so many have weights (and tiles)."""
     n_x, K = x_rows.shape
     n_pairs = sorted_pair.numel()
     N = out.shape[1]
-    want = (n_experts, 2 * N, K) if mode == 1 else (n_experts, N, K)
+    n_w = weight_experts or n_experts
+    want = (n_w, 2 * N, K) if mode == 1 else (n_w, N, K)
     if tuple(weights.shape) != want:
         raise ValueError(f"expert_gemm_tc: weights {tuple(weights.shape)} != {want}")
     if gather_top_k == 0 and n_x != n_pairs:
@@ -527,7 +580,8 @@ def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, t
     _want(out, torch.float32 if mode == 2 else torch.bfloat16, "out")
     _check(lib().qb_expert_gemm_tc(mode, _p(x_rows), _p(weights), _p(out), _p(sorted_pair), _p(pair_w), _p(plan),
                                    _p(tile_expert), _p(tile_row0), tile_expert.numel(), n_pairs, n_experts, K, N,
-                                   int(tile_rows), int(gather_top_k), n_x, _p(status), _stream()), "expert_gemm_tc")
+                                   int(tile_rows), int(gather_top_k), n_x, _p(status), int(weight_experts), _stream()),
+           "expert_gemm_tc")
 
 
 # ---- state slots (csrc/request_state.h) ------------------------------------------------------------------
@@ -599,18 +653,26 @@ def apply_penalties(logits, prev, prev_off, pparams) -> None:
 
 
 # ---- short convolution, delta-rule recurrence, latent attention ---------------------------------------
-def short_conv(x, weight, state, out, tok_req, req_start, req_slot) -> None:
+def short_conv(x, weight, state, out, tok_req, req_start, req_slot, *, bias=None, silu: bool = False) -> None:
     """``out[t] = x[t] + sum_j weight[:, j] * x[t - taps + 1 + j]`` over each request's own rows, the rows
     before a portion taken from ``state`` ``[slots, taps - 1, C]`` (float32, newest last), which then holds
-    the request's last ``taps - 1`` inputs.  ``x`` float32 ``[T, C]``, ``weight`` float32 ``[C, taps]``."""
+    the request's last ``taps - 1`` inputs.  ``x`` float32 ``[T, C]`` (a column range of wider rows is fine),
+    ``weight`` float32 ``[C, taps]``.  ``silu``: ``out[t] = silu(bias + sum_j ...)`` instead, the input not added back."""
     _want(x, torch.float32, "x"); _want(weight, torch.float32, "weight"); _want(state, torch.float32, "state")
     T, C = x.shape
     taps = weight.shape[1]
     if weight.shape[0] != C or tuple(out.shape) != (T, C) or tuple(state.shape[1:]) != (max(taps - 1, 0), C):
         raise ValueError("short_conv: shape mismatch")
+    if x.stride(1) != 1 or not weight.is_contiguous() or not out.is_contiguous() or not state.is_contiguous():
+        raise ValueError("short_conv: rows must be contiguous")
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+        if bias.numel() != C or not silu:
+            raise ValueError("short_conv: the bias has C numbers and belongs to the silu form")
     R = req_slot.numel()
-    _check(lib().qb_short_conv(_p(x), _p(weight), _p(state), _p(out), _code(out), _p(tok_req), _p(req_start),
-                               _p(req_slot), T, R, C, taps, _stream()), "short_conv", 2 if taps > 1 else 1)
+    _check(lib().qb_short_conv(ctypes.c_void_p(x.data_ptr()), _p(weight), _p(state), _p(out), _code(out), _p(tok_req),
+                               _p(req_start), _p(req_slot), T, R, C, taps, int(x.stride(0)), _p(bias), int(silu),
+                               _stream()), "short_conv", 2 if taps > 1 else 1)
 
 
 DELTA_RULE_MAX_DIM = 256
@@ -770,3 +832,84 @@ def latent_attend(q_lat, q_rot, cache, sink, out, tok_pos, tok_req, block_table,
                "latent_attend")
     _check(lib().qb_latent_merge(_p(part), _p(sink), _p(out), _code(out), T, H, C, int(n_ranges), _stream()),
            "latent_merge")
+
+
+# ---- sliding-window attention with extras (csrc/window_attention.cu) ---------------------------------------------
+def window_attention(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, scale: float, window: int, status, *,
+                     dist_bias=None, sink=None, softcap: float = 0.0, pool: int = 0, pooled_k=None, pooled_v=None,
+                     pool_table=None, talk=None, scratch=None) -> None:
+    """Softmax attention of every token over the last ``window`` keys of its request (0: all of them).  Options:
+    ``dist_bias`` float32 ``[window, heads]`` added to the score by distance; ``sink`` float32 ``[heads]``, a term
+    ``exp(sink)`` of the denominator; ``softcap`` c > 0: ``score <- c tanh(score / c)``; ``pool`` P with the pooled
+    pages and their block table: one more key and value per block of P tokens that lies wholly before the window;
+    ``talk`` float32 ``[heads, heads]``: the heads' softmax weights are mixed, ``w'_h = sum_g talk[h, g] w_g``
+    (``scratch`` float32 ``[T, heads, kv heads, vd]``).  float32 arithmetic; q, caches and out in one dtype."""
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    vd = v_cache.shape[3]
+    if hd2 != hd or tuple(out.shape) != (T, nq, vd) or out.dtype != q.dtype or k_cache.dtype != q.dtype:
+        raise ValueError("window_attention: shape/dtype mismatch")
+    n_pool_pages = 0
+    if pool_table is not None:
+        if pool <= 0 or pooled_k is None or pooled_v is None or tuple(pooled_k.shape[1:]) != (nkv, page_size, hd) \
+                or tuple(pooled_v.shape[1:]) != (nkv, page_size, vd) or pooled_k.dtype != q.dtype:
+            raise ValueError("window_attention: the pooled pages do not fit")
+        _want(pool_table, torch.int32, "pool_table")
+        n_pool_pages = pooled_k.shape[0]
+    if dist_bias is not None:
+        _want(dist_bias, torch.float32, "dist_bias")
+        if tuple(dist_bias.shape) != (window, nq):
+            raise ValueError("window_attention: dist_bias must be [window, heads]")
+    if sink is not None:
+        _want(sink, torch.float32, "sink")
+        if sink.numel() != nq:
+            raise ValueError("window_attention: sink must have one number a head")
+    if talk is not None:
+        _want(talk, torch.float32, "talk"); _want(scratch, torch.float32, "scratch")
+        if tuple(talk.shape) != (nq, nq) or scratch.numel() < T * nq * nkv * vd:
+            raise ValueError("window_attention: talk must be [heads, heads] and scratch [T, heads, kv heads, vd]")
+    _check(lib().qb_window_attention(
+        _p(q), _code(q), _p(k_cache), _p(v_cache), _p(pooled_k), _p(pooled_v), _p(out), _p(scratch), _p(talk),
+        _p(tok_pos), _p(tok_req), _p(block_table), block_table.shape[1], _p(pool_table),
+        pool_table.shape[1] if pool_table is not None else 0, T, nq, nkv, hd, vd, page_size, num_pages, n_pool_pages,
+        ctypes.c_float(scale), ctypes.c_float(softcap), int(window), int(pool), _p(dist_bias), _p(sink), _p(status),
+        _stream()), "window_attention", 2 if talk is not None else 1)
+
+
+def pool_blocks(k_cache, v_cache, pooled_k, pooled_v, tok_pos, tok_req, block_table, pool_table, pool: int, status) -> None:
+    """Every token of the step whose position ends a block of ``pool`` tokens leaves the mean key and mean value of
+    the block (as the cache holds them) in row ``position // pool`` of the pooled pages."""
+    num_pages, nkv, page_size, hd = k_cache.shape
+    vd = v_cache.shape[3]
+    if tuple(pooled_k.shape[1:]) != (nkv, page_size, hd) or tuple(pooled_v.shape[1:]) != (nkv, page_size, vd) \
+            or pooled_k.dtype != k_cache.dtype:
+        raise ValueError("pool_blocks: the pooled pages do not fit")
+    _check(lib().qb_pool_blocks(_p(k_cache), _p(v_cache), _p(pooled_k), _p(pooled_v), _code(k_cache), _p(tok_pos),
+                                _p(tok_req), _p(block_table), block_table.shape[1], _p(pool_table), pool_table.shape[1],
+                                tok_pos.numel(), nkv, hd, vd, page_size, num_pages, pooled_k.shape[0], int(pool),
+                                _p(status), _stream()), "pool_blocks")
+
+
+# ---- selective state-space scan (csrc/selective_scan.cu) ----------------------------------------------------------
+SCAN_MAX_STATE = 256
+
+
+def selective_scan(u, proj, z, w_dt, dt_bias, A, D, state, out, req_start, req_slot, rank: int, n_state: int) -> None:
+    """``S <- exp(dt A) S + dt u B``, ``y = S C + D u``, ``out = y * silu(z)`` per channel over each request's rows, with
+    ``dt = softplus(w_dt low + dt_bias)``.  ``u`` ``[T, inner]`` in the activation dtype; ``proj`` float32 rows
+    ``[low (rank) | B (n_state) | C (n_state)]``; ``z`` float32 ``[T, inner]`` (a column range of wider rows is fine);
+    ``w_dt`` float32 ``[inner, rank]``; ``A`` float32 ``[inner, n_state]`` (negative); ``state`` float32
+    ``[slots, inner, n_state]``, read and left updated at the rows ``req_slot``."""
+    T, inner = u.shape
+    for t, n in ((proj, "proj"), (z, "z"), (w_dt, "w_dt"), (dt_bias, "dt_bias"), (A, "A"), (D, "D"), (state, "state")):
+        _want(t, torch.float32, n)
+    if (proj.shape[0] != T or proj.shape[1] < rank + 2 * n_state or proj.stride(1) != 1 or tuple(z.shape) != (T, inner)
+            or z.stride(1) != 1 or tuple(w_dt.shape) != (inner, rank) or tuple(A.shape) != (inner, n_state)
+            or D.numel() != inner or dt_bias.numel() != inner or tuple(state.shape[1:]) != (inner, n_state)
+            or tuple(out.shape) != (T, inner) or out.dtype != u.dtype):
+        raise ValueError("selective_scan: shape mismatch")
+    dt = torch.empty((T, inner), dtype=torch.float32, device=u.device)
+    _check(lib().qb_selective_scan(_p(u), _code(u), ctypes.c_void_p(proj.data_ptr()), int(proj.stride(0)),
+                                   ctypes.c_void_p(z.data_ptr()), int(z.stride(0)), _p(w_dt), _p(dt_bias), _p(A), _p(D),
+                                   _p(state), _p(dt), _p(out), _p(req_start), _p(req_slot), T, req_slot.numel(), inner,
+                                   int(n_state), int(rank), _stream()), "selective_scan", 2)

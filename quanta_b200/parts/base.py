@@ -58,7 +58,7 @@ class TensorSpec:
     held in float32 whatever the compute dtype (norm gains, router gate and bias: a tensor stored in
     32-bit stays so); ``"i32"`` integer tables.  ``init`` tells the random-weights mode how to draw
     it: ``"normal"`` N(0, 0.02), ``"gain"`` 1 + U(-0.1, 0.1), ``"bias"`` U(-0.05, 0.05), ``"mixing"`` a square matrix, the
-    identity + U(-0.1, 0.1).
+    identity + U(-0.1, 0.1), ``"fraction"`` U(0.2, 0.8).
     """
     name: str
     shape: tuple[int, ...]
@@ -103,11 +103,27 @@ class Window(Retention):
 
 
 @dataclass(frozen=True)
+class WindowAndOpenBlock(Retention):
+    """A window, and besides the tokens of the block of ``block`` tokens that is not whole yet (a mixer that
+    summarises every whole block from the pages reads them once more when the block's last token arrives)."""
+    window: int = 1
+    block: int = 1
+
+    def needed_ranges(self, length):
+        return [(max(0, min(length - self.window + 1, length // self.block * self.block)), None)]
+
+
+@dataclass(frozen=True)
 class CacheSpec:
     """A mixer's need of paged per-token storage: its streams and what is retained.  Layers with equal
-    specs form one group of the cache manager: they share pages ids and block tables."""
+    specs form one group of the cache manager: they share pages ids and block tables.  ``stride`` > 1: the
+    streams hold one row per ``stride`` tokens (row ``p // stride`` belongs to position ``p``: a summary of
+    every block of that many tokens), so a page of ``page_size`` rows covers ``page_size * stride`` positions;
+    the retention rule still speaks of token positions.  A mixer that keeps rows per token and rows per block
+    declares two specs (``Mixer.cache_spec`` may return a tuple); every stream of a mixer has its own name."""
     streams: tuple[CacheStream, ...]
     retention: Retention = KeepAll()
+    stride: int = 1
 
     @property
     def window(self) -> int | None:
@@ -125,11 +141,15 @@ class LayerCache:
     """What a mixer sees of the cache in one step: its own pages of every stream it declared
     (``streams[name]`` ``[num_pages, heads, page_size, width]``) and its group's block table (int32
     ``[requests in the step, pages per request]``, -1 where a page was given back).  ``write`` False:
-    this layer reads a cache another layer wrote.  ``k`` / ``v`` are the streams of those names."""
+    this layer reads a cache another layer wrote.  ``k`` / ``v`` are the streams of those names.  A mixer
+    with several cache specs finds the block table of each stream's group in ``tables[name]``
+    (``block_table`` is the first spec's)."""
 
-    def __init__(self, k=None, v=None, page_size: int = 0, block_table=None, write: bool = True, streams=None):
+    def __init__(self, k=None, v=None, page_size: int = 0, block_table=None, write: bool = True, streams=None,
+                 tables=None):
         self.streams = dict(streams) if streams is not None else {"k": k, "v": v}
         self.page_size, self.block_table, self.write = page_size, block_table, write
+        self.tables = dict(tables) if tables is not None else {name: block_table for name in self.streams}
 
     @property
     def k(self):
@@ -189,19 +209,53 @@ class Part:
         return []
 
 
+class Addends:
+    """A sublayer's output as a sum that nobody has taken yet:
+    ``scale * (sum_s y[:, s] + bias) + extra_scale * (extra + extra_bias)`` with ``y`` float32 ``[T, H]`` or
+    ``[T, S, H]``, ``extra`` float32 ``[T, H]`` or None and biases of ``H`` numbers or None.  A mixer or feed-forward
+    whose block norms its output may return one instead of a tensor: the norm kernel that reads the output takes
+    the sum in the same launch (an output bias, two branches with a weight each, routed slots and a shared expert)."""
+
+    def __init__(self, y, scale: float = 1.0, bias=None, extra=None, extra_scale: float = 1.0, extra_bias=None):
+        self.y, self.scale, self.bias = y, float(scale), bias
+        self.extra, self.extra_scale, self.extra_bias = extra, float(extra_scale), extra_bias
+
+    def total(self) -> torch.Tensor:
+        """The sum as a float32 ``[T, H]`` tensor (plain torch; for tools, not for the step)."""
+        y = self.y.float()
+        z = y.sum(1) if y.dim() == 3 else y.clone()
+        if self.bias is not None:
+            z += self.bias
+        z *= self.scale
+        if self.extra is not None:
+            e = self.extra.float() + (self.extra_bias if self.extra_bias is not None else 0.0)
+            z += self.extra_scale * e
+        return z
+
+
 class NormedPending:
     """A pending contribution that is normed before it joins the residual stream: ``y`` (float32 ``[T, H]``, a
-    sublayer's output) and the norm part that is applied to it.  A norm that gets one as its ``delta`` norms
-    ``y``, adds it and norms the sum in one launch when it can (``Norm.forward`` of the built-in norms); whoever
-    needs the plain numbers calls ``materialize``."""
+    sublayer's output, or an ``Addends`` whose sum is that output) and the norm part that is applied to it.  A norm
+    that gets one as its ``delta`` norms ``y``, adds it and norms the sum in one launch when it can
+    (``Norm.forward`` of the built-in norms); whoever needs the plain numbers calls ``materialize``."""
 
-    def __init__(self, y: torch.Tensor, norm: "Norm"):
-        self.y = y if y.dtype == torch.float32 else y.float()
+    def __init__(self, y, norm: "Norm"):
+        if isinstance(y, Addends):
+            self.addends = y
+        else:
+            self.addends = Addends(y if y.dtype == torch.float32 else y.float())
         self.norm = norm
 
+    @property
+    def y(self) -> torch.Tensor:
+        a = self.addends
+        plain = a.y.dim() == 2 and a.scale == 1.0 and a.bias is None and a.extra is None
+        return a.y if plain else a.total()
+
     def materialize(self) -> torch.Tensor:
-        d = torch.empty(self.y.shape, dtype=torch.float32, device=self.y.device)
-        self.norm.forward(self.y, None, d)
+        y = self.y
+        d = torch.empty(y.shape, dtype=torch.float32, device=y.device)
+        self.norm.forward(y, None, d)
         return d
 
 
@@ -239,8 +293,9 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_spec(self) -> CacheSpec | None:
-        """What the mixer keeps per token in pages (streams and retention); None: nothing."""
+    def cache_spec(self) -> CacheSpec | tuple[CacheSpec, ...] | None:
+        """What the mixer keeps per token in pages (streams and retention); None: nothing.  A tuple: several
+        needs with different retention or stride, each a page group of its own."""
         return None
 
     def state_spec(self) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:

@@ -18,7 +18,7 @@ import os
 import torch
 
 from .. import kernels
-from .base import FeedForward, TensorSpec, register
+from .base import Addends, FeedForward, TensorSpec, register
 
 
 @register("feed_forward", "sigmoid_topk_experts")
@@ -46,6 +46,7 @@ class SigmoidTopKExperts(FeedForward):
         self.H, self.I, self.E, self.k = int(hidden_size), int(expert_size), int(n_experts), int(top_k)
         self.use_bias, self.renorm, self.scaling = bool(use_bias), bool(renormalize), float(scaling)
         self.names = dict(names)   # gate, bias, and templates w1/w2/w3 with "{e}"
+        self.E_w = self.E          # experts that have weights (a subclass may route to some that have none)
         self.gate_w = self.bias = self.w13 = self.w2 = self.gate_pieces = None
         self.last_counts = None      # rows per expert in the last step (device tensor; for measurements)
         self._plan_counter = None    # the router kernel's counters of finished blocks (zero at rest)
@@ -152,9 +153,11 @@ class SigmoidTopKExperts(FeedForward):
                 self._plan_counter = torch.zeros(max(64, 1 + -(-T // 8)), dtype=torch.int32, device=dev)
             kernels.router_small(x, self.gate_w, self.bias, logits, idx, w, self.renorm, self.scaling,
                                  counters=self._plan_counter, bm=bm, plan=plan, sorted_pair=sorted_pair,
-                                 tile_expert=tile_expert, tile_row0=tile_row0, status=ctx.status)
+                                 tile_expert=tile_expert, tile_row0=tile_row0, status=ctx.status,
+                                 tiled_experts=self.E_w)
         else:
-            kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
+            kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status,
+                             tiled_experts=self.E_w)
         self.last_counts = plan[: self.E]
         if self.trace is not None:
             self.trace.append(idx)
@@ -165,19 +168,23 @@ class SigmoidTopKExperts(FeedForward):
             if n_pairs <= self.gather_in_kernel_max_rows * self.E:
                 # few tokens: the kernel fetches each pair's token row itself
                 kernels.expert_gemm_tc(self.first_product_mode, x, self.w13, act, sorted_pair, w.view(-1), plan,
-                                       tile_expert, tile_row0, self.E, bm, ctx.status, gather_top_k=self.k)
+                                       tile_expert, tile_row0, self.E, bm, ctx.status, gather_top_k=self.k,
+                                       weight_experts=self.E_w)
             else:
                 xg = torch.empty((n_pairs, self.H), dtype=x.dtype, device=dev)
                 kernels.gather_rows(x, xg, sorted_pair, self.k)
                 kernels.expert_gemm_tc(self.first_product_mode, xg, self.w13, act, sorted_pair, w.view(-1), plan,
-                                       tile_expert, tile_row0, self.E, bm, ctx.status)
+                                       tile_expert, tile_row0, self.E, bm, ctx.status, weight_experts=self.E_w)
             kernels.expert_gemm_tc(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
-                                   tile_expert, tile_row0, self.E, bm, ctx.status)
+                                   tile_expert, tile_row0, self.E, bm, ctx.status, weight_experts=self.E_w)
         else:
             kernels.moe_grouped_simt(self.first_product_mode, x, self.w13, act, sorted_pair, w, plan, tile_expert,
                                      tile_row0, self.E, self.k)
             kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
                                      tile_expert, tile_row0, self.E, self.k)
+        if self.E_w < self.E:
+            # the chosen experts past the last one with weights hand the token through, times its weight
+            kernels.identity_slots(x, idx, w, y, self.E_w)
         return y
 
 
@@ -216,3 +223,67 @@ class SoftmaxTopKExperts(SigmoidTopKExperts):
         del first
         if dt == torch.bfloat16 and self.H % 8 == 0 and self.gate_w.is_cuda:
             self.gate_pieces = kernels.split3_bf16(self.gate_w)
+
+
+@register("feed_forward", "softmax_shared_experts")
+class SoftmaxSharedExperts(SigmoidTopKExperts):
+    """Routed gated experts whose router scores are the softmax over ALL router outputs: the ``top_k`` largest of
+    ``score + correction`` choose (the lower index among equals), and the weights are the chosen scores as they are
+    (not renormalised).  The last ``n_identity`` router outputs stand for experts without weights that return their
+    input.  ``shared_size`` > 0: a gated expert of that inner size that every token passes is added.  An expert is
+    ``down(silu(gate x) * (up x))`` without biases.  ``names``: gate (the router, ``[n_experts + n_identity,
+    hidden]``), bias (the correction), templates w1 / w3 / w2 with ``{e}`` (an expert's gate, up, down), and
+    shared_gate / shared_up / shared_down.  Returns the routed slots with the shared expert's output as a second
+    addend, for a block that norms the sum."""
+
+    def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top_k: int, names: dict, n_identity: int = 0,
+                 shared_size: int = 0, use_bias: bool = True):
+        if n_identity < 0 or n_experts < 0 or n_experts + n_identity < 1:
+            raise ValueError(f"{n_experts} experts and {n_identity} identity experts")
+        super().__init__(hidden_size, expert_size, n_experts + n_identity, top_k, use_bias, renormalize=False,
+                         scaling=1.0, names=names)
+        self.E_w = int(n_experts)
+        self.renorm = kernels.ROUTE_SOFTMAX_ALL
+        self.shared_size = int(shared_size)
+        self.shared = None
+        if self.shared_size:
+            from .dense import GatedDense
+            self.shared = GatedDense(hidden_size, shared_size, {"gate": names["shared_gate"], "up": names["shared_up"],
+                                                                "down": names["shared_down"]})
+
+    def children(self):
+        return [self.shared] if self.shared is not None else []
+
+    def tensor_specs(self):
+        n = self.names
+        specs = [TensorSpec(n["gate"], (self.E, self.H), "f32", "normal")]
+        if self.use_bias:
+            specs.append(TensorSpec(n["bias"], (self.E,), "f32", "bias"))
+        for e in range(self.E_w):
+            specs += [TensorSpec(n["w1"].format(e=e), (self.I, self.H)), TensorSpec(n["w3"].format(e=e), (self.I, self.H)),
+                      TensorSpec(n["w2"].format(e=e), (self.H, self.I))]
+        return specs
+
+    def load(self, fetch):
+        n = self.names
+        self.gate_w = fetch(n["gate"])
+        self.bias = fetch(n["bias"]) if self.use_bias else None
+        dt, dev = self.gate_w.dtype, self.gate_w.device
+        if self.E_w:
+            first = fetch(n["w1"].format(e=0))
+            dt = first.dtype
+            self.w13 = torch.empty((self.E_w, 2 * self.I, self.H), dtype=dt, device=dev)
+            self.w2 = torch.empty((self.E_w, self.H, self.I), dtype=dt, device=dev)
+            for e in range(self.E_w):
+                self.w13[e, : self.I].copy_(first if e == 0 else fetch(n["w1"].format(e=e)))
+                self.w13[e, self.I:].copy_(fetch(n["w3"].format(e=e)))
+                self.w2[e].copy_(fetch(n["w2"].format(e=e)))
+            del first
+        if dt == torch.bfloat16 and self.H % 8 == 0 and self.gate_w.is_cuda:
+            self.gate_pieces = kernels.split3_bf16(self.gate_w)
+
+    def forward(self, x, ctx):
+        y = super().forward(x, ctx)
+        if self.shared is None:
+            return Addends(y)
+        return Addends(y, extra=self.shared.forward(x, ctx))

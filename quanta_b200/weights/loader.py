@@ -74,7 +74,7 @@ class RandomSource:
     bfloat16 directly on the GPU), so the order of generation does not matter, and the same seed on the same
     kind of device gives the same model; a folder written by the random-weights mode (drawn on the CPU) and a
     model drawn on the GPU from the same seed are two different models.  ``normal``: N(0, 0.02); ``gain``: 1 + U(-0.1, 0.1); ``bias``:
-    U(-0.05, 0.05); ``mixing``: the identity + U(-0.1, 0.1).  Matrices are drawn in float32 and rounded to ``matrix_dtype``."""
+    U(-0.05, 0.05); ``mixing``: the identity + U(-0.1, 0.1); ``fraction``: U(0.2, 0.8).  Matrices are drawn in float32 and rounded to ``matrix_dtype``."""
 
     def __init__(self, specs: Iterable[TensorSpec], seed: int, matrix_dtype=torch.bfloat16):
         self.specs = {s.name: s for s in specs}
@@ -110,6 +110,8 @@ class RandomSource:
             # a square matrix near the identity: what mixes residual streams must not blow them up
             t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(-0.1, 0.1, generator=g)
             t += torch.eye(s.shape[0], dtype=torch.float32, device=device)
+        elif s.init == "fraction":
+            t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(0.2, 0.8, generator=g)
         else:
             raise ValueError(f"{name}: unknown init {s.init!r}")
         return t.to(self.matrix_dtype) if s.kind == "matrix" else t
