@@ -94,9 +94,9 @@ class TarulixConfig:
                 _check_heads(f"layers[{i}].mixer", m)
                 if "bias_max" not in m:
                     raise ConfigError(f"layers[{i}].mixer lacks 'bias_max'")
-                rows = int(m.get("bias_rows", DEFAULT_BIAS_ROWS))
-                if rows < 1 or (rows > 1 and float(m["bias_max"]) <= rows // 2):
-                    raise ConfigError(f"layers[{i}].mixer: a bias of {rows} rows needs bias_max beyond {rows // 2}")
+                rows = m.get("bias_rows")                     # known once a checkpoint has been opened
+                if rows is not None and (int(rows) < 1 or (int(rows) > 1 and float(m["bias_max"]) <= int(rows) // 2)):
+                    raise ConfigError(f"layers[{i}].mixer: a bias of {rows} rows needs bias_max beyond {int(rows) // 2}")
                 if m.get("v_mix"):
                     shape = (int(m["kv_heads"]), int(m["vdim"]))
                     if blend_shape is not None and shape != blend_shape:

@@ -86,7 +86,7 @@ class Model:
         return out
 
     def load(self, source) -> "Model":
-        ignorable = ("lm_head.weight",) if self.spec.tied_head else ()
+        ignorable = (("lm_head.weight",) if self.spec.tied_head else ()) + tuple(self.spec.ignorable_names)
         fetch = open_fetch(source, self.tensor_specs(), compute_dtype=self.dtype, device=self.device,
                            aliases=self.spec.name_aliases, ignored_prefixes=self.spec.ignored_prefixes,
                            ignorable=ignorable)

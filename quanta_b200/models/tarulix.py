@@ -30,11 +30,16 @@ def biased_attention(cfg: TarulixConfig, i: int, m: dict, first_blend: int | Non
     blend = None
     if m.get("v_mix"):
         blend = "source" if first_blend == i else "blend"
+    rows = m.get("bias_rows")
+    if rows is None:                       # no checkpoint: as many rows as the ladder's end allows
+        rows = DEFAULT_BIAS_ROWS
+        while rows > 2 and float(m["bias_max"]) <= rows // 2:
+            rows //= 2
     return ("window_attention", dict(
         hidden_size=cfg.width, n_q_heads=int(m["heads"]), n_kv_heads=int(m["kv_heads"]), head_dim=int(m["dim"]),
         value_dim=int(m["vdim"]), scale=float(m["scale"]), window=int(m["mask"]["size"]), norm_eps=cfg.norm_eps,
         names=_attention_names(f"l{i}.mix."), position=("none", {}), unit_qk=True, biases=True,
-        distance_bias=(int(m.get("bias_rows", DEFAULT_BIAS_ROWS)), float(m["bias_max"])), sink=True,
+        distance_bias=(int(rows), float(m["bias_max"])), sink=True,
         value_blend=blend, blend_key=BLEND_KEY))
 
 
@@ -92,10 +97,14 @@ def build_spec(cfg: TarulixConfig) -> ModelSpec:
     blending = [i for i, l in enumerate(cfg.layers) if l.type == "attention" and l.mixer.get("v_mix")]
     first_blend = blending[0] if blending else None
     final_norm = ("rms_norm", dict(width=cfg.width, eps=cfg.norm_eps, weight_name="final.norm", scalar_gain=True))
+    # a checkpoint may hold a blending fraction for attention layers that blend nothing (the first of the chain and
+    # layers outside it)
+    unused = tuple(f"l{i}.mix.vmix" for i, l in enumerate(cfg.layers)
+                   if l.type == "attention" and (i == first_blend or not l.mixer.get("v_mix")))
     return ModelSpec(
         name="Tarulix", vocab_size=cfg.vocab, hidden_size=cfg.width, embedding_name="embed",
         layers=[layer_choice(cfg, i, first_blend) for i in range(len(cfg.layers))],
-        final_norm=final_norm, head_name="head", tied_head=False)
+        final_norm=final_norm, head_name="head", tied_head=False, ignorable_names=unused)
 
 
 ARCHITECTURE = register_architecture(["Tarulix", "tarulix"], TarulixConfig, build_spec)

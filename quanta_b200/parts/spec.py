@@ -31,6 +31,7 @@ class ModelSpec:
     tied_head: bool = False
     schedule: list[ScheduleEntry] = field(default_factory=list)
     ignored_prefixes: tuple[str, ...] = ()     # checkpoint tensors that are not this model's and are skipped
+    ignorable_names: tuple[str, ...] = ()      # tensors a checkpoint may hold that the model does not use
     name_aliases: tuple[tuple[str, str], ...] = ()   # (prefix in file, prefix in spec) rewrites
     # ("embedding part name", params) and ("head part name", params); None: the token table and the
     # normed linear head described by the fields above

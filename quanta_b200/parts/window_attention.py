@@ -20,7 +20,7 @@ Each extra is a parameter and is off unless it is given:
   head h applies ``w'_h`` to the values of its own kv head.
 * ``value_blend``: ``"source"``: the layer leaves its values (per token of the step, float32) under ``blend_key``
   for later layers; ``"blend"``: its values become ``(1 - lambda) v + lambda v_source`` with the learned number
-  ``vmix`` before they are cached.  A source layer still owns a ``vmix`` tensor, which it does not use.
+  ``vmix`` before they are cached.  A source layer has no fraction of its own.
 
 Scores, softmax weights, the bias, the sink and the mixing of heads are float32; the projections' float32
 accumulators (with the biases) feed the kernel that norms, rotates and fills the cache.
@@ -95,7 +95,7 @@ class WindowAttention(Mixer):
                       TensorSpec(n["v_b"], (self.nkv * vd,), "f32", "bias"), TensorSpec(n["o_b"], (W,), "f32", "bias")]
         if self.distance_bias is not None:
             specs.append(TensorSpec(n["rel"], (self.distance_bias[0], self.nq), "f32", "bias"))
-        if self.value_blend is not None:
+        if self.value_blend == "blend":
             specs.append(TensorSpec(n["vmix"], (), "f32", "fraction"))
         if self.has_sink:
             specs.append(TensorSpec(n["sink"], (self.nq,), "f32", "bias"))
@@ -124,9 +124,8 @@ class WindowAttention(Mixer):
             rel = fetch(n["rel"])
             rows_of = distance_buckets(self.window, *self.distance_bias)
             self.dist_table = rel[torch.tensor(rows_of, dtype=torch.long, device=rel.device)].contiguous()
-        if self.value_blend is not None:
-            lam = fetch(n["vmix"])                      # a source layer owns one too, and does not use it
-            self.lam = lam.reshape(1).contiguous() if self.value_blend == "blend" else None
+        if self.value_blend == "blend":
+            self.lam = fetch(n["vmix"]).reshape(1).contiguous()
         if self.has_sink:
             self.sink = fetch(n["sink"]).contiguous()
         if self.has_talk:

@@ -84,7 +84,7 @@ def write_safetensors(path, tensors: dict[str, torch.Tensor]) -> None:
         t = t.detach().contiguous().cpu()
         if t.dtype not in _NAMES:
             raise ValueError(f"{name}: dtype {t.dtype} cannot be stored")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)
