@@ -1,4 +1,4 @@
-"""``bench.py --design guravik`` / ``--design tirizen``: another decoder beside the MiniMax-M3 decoder at equal sizes.
+"""``bench.py --design guravik`` / ``--design tirizen`` / ``--design tarulix``: another decoder beside the MiniMax-M3 decoder at equal sizes.
 
 For a few sizes that resemble a real model's layers (seeded random weights, bfloat16): one prompt of
 ``--prompt-len`` tokens as one step (tokens a second) and decode steps of ``--batch`` requests at that
@@ -20,6 +20,12 @@ three residual streams), whose attention and expert products run on the SAME ker
 sizes; alone are measured the kernels that are its own: the gated linear recurrence beside Guravik's delta-rule
 recurrence (the like kernel), and the launch between two sublayers (streams written back, read and normed)
 beside the adding RMS norm, both as bytes / time / copy bandwidth.
+
+``--design tarulix``: the same two model measurements for the Tarulix decoder (layers: two windowed attentions with
+distance bias, sink and blended values, then a rotary windowed attention with pooled blocks beside a selective scan;
+routed, pass-through and shared experts).  Alone: ``window_attention`` in both forms over a prompt (flops / time /
+tensor peak) and over single tokens deep in a context (visible cache bytes / time / copy bandwidth) beside the
+softmax-attention kernels of MiniMax-M3, and ``selective_scan`` beside Tirizen's gated linear recurrence.
 """
 
 from __future__ import annotations
@@ -72,6 +78,34 @@ def tirizen_raw(s: dict) -> dict:
     return {"architecture": "Tirizen", "vocab": s["vocab"], "width": s["width"], "layers": layers, "streams": s["streams"],
             "residual_mult": 0.8, "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-5},
             "max_positions": 8192}
+
+
+TARULIX_SIZES = {
+    "w2048": dict(width=2048, groups=2, vocab=32000, ff=5632, attn_heads=16, dim=128, window=1024, pool=64, rot=64, inner=4096,
+                  state=16, dt_rank=128, taps=4),
+    "w4096": dict(width=4096, groups=2, vocab=32000, ff=11008, attn_heads=32, dim=128, window=1024, pool=64, rot=64, inner=8192,
+                  state=16, dt_rank=256, taps=4),
+}
+
+
+def tarulix_raw(s: dict) -> dict:
+    """Per group of three layers: two windowed attention layers with distance bias, sink and blended values, then a
+    rotary windowed attention with pooled blocks beside a selective scan; every layer with 8 routed experts and 2
+    pass-through experts of which 2 are chosen, and a shared expert: two routed experts and the shared one are
+    together as wide as ``ff``."""
+    moe = {"kind": "moe", "expert": {"ff": 3 * s["ff"] // 8}, "router": {"experts": 8, "identity": 2, "top": 2},
+           "shared": {"ff": s["ff"] // 4}}
+    heads = {"heads": s["attn_heads"], "kv_heads": max(1, s["attn_heads"] // 4), "dim": s["dim"], "vdim": s["dim"],
+             "scale": 1.0 / math.sqrt(s["dim"])}
+    attn = dict(heads, mask={"size": s["window"]}, bias_max=4 * s["window"], v_mix=True)
+    left = dict(heads, mask={"size": s["window"], "pool": s["pool"]}, rot={"dims": s["rot"], "base": 1e6}, softcap=30.0)
+    right = {"inner": s["inner"], "state": s["state"], "dt_rank": s["dt_rank"], "conv": s["taps"]}
+    layers = []
+    for _ in range(s["groups"]):
+        layers += [{"type": "attention", "mixer": dict(attn), "mlp": moe}, {"type": "attention", "mixer": dict(attn), "mlp": moe},
+                   {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right), "left_scale": 0.8, "right_scale": 0.9},
+                    "mlp": moe}]
+    return {"architecture": "Tarulix", "vocab": s["vocab"], "width": s["width"], "layers": layers, "norm": {"eps": 1e-5}}
 
 
 def minimax_raw(s: dict) -> dict:
@@ -299,9 +333,139 @@ def run_tirizen(args) -> dict:
             "gpu_launches": first.get("launches_per_decode_step", 0) * args.steps, "impl": "ours"}
 
 
+def window_attn(tokens_per_req: int, reqs: int, context: int, nq: int, nkv: int, hd: int, window: int, kind: str,
+                pool: int = 64, page: int = 16) -> dict:
+    """``window_attention`` alone: ``reqs`` requests whose last ``tokens_per_req`` tokens (ending at ``context``) are
+    the step.  ``kind`` "biased": distance bias and sink; "pooled": score cap, pooled blocks and mixed head weights
+    (with the second launch that mixes).  Flops count ``4 * head_dim`` a (query head, visible key), pooled rows too;
+    bytes count the visible keys and values once a request."""
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    per = -(-context // page)
+    single = tokens_per_req == 1
+    layers = 1 if not single else max(1, min(16, int(3e9 // (2 * reqs * per * nkv * page * hd * 2))))
+    caches = [(torch.randn(reqs * per, nkv, page, hd, device=dev, dtype=torch.bfloat16),
+               torch.randn(reqs * per, nkv, page, hd, device=dev, dtype=torch.bfloat16)) for _ in range(layers)]
+    table = torch.randperm(reqs * per, dtype=torch.int32).view(reqs, per).to(dev)
+    T = tokens_per_req * reqs
+    q = torch.randn(T, nq, hd, device=dev, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.arange(context - tokens_per_req, context, dtype=torch.int32, device=dev).repeat(reqs)
+    req = torch.arange(reqs, dtype=torch.int32, device=dev).repeat_interleave(tokens_per_req)
+    st = k.new_status(dev)
+    extras = {}
+    if kind == "biased":
+        extras = dict(dist_bias=torch.randn(window, nq, device=dev), sink=torch.zeros(nq, device=dev))
+    else:
+        rows = -(-context // pool)
+        ppp = -(-rows // page)
+        extras = dict(softcap=30.0, pool=pool, pooled_k=torch.randn(reqs * ppp, nkv, page, hd, device=dev, dtype=torch.bfloat16),
+                      pooled_v=torch.randn(reqs * ppp, nkv, page, hd, device=dev, dtype=torch.bfloat16),
+                      pool_table=torch.randperm(reqs * ppp, dtype=torch.int32).view(reqs, ppp).to(dev),
+                      talk=torch.eye(nq, device=dev) + 0.1 * torch.randn(nq, nq, device=dev),
+                      scratch=torch.empty(T, nq, nkv, hd, device=dev))
+
+    def all_layers():
+        for kc, vc in caches:
+            k.window_attention(q, kc, vc, out, pos, req, table, hd ** -0.5, window, st, n_requests=reqs, **extras)
+    ms = (bk.timed_graph(all_layers, reps=1) if single else bk.timed(all_layers, n=5, warm=2)) / layers
+    k.raise_on_status(st.cpu())
+    seen = 0
+    for p_ in range(context - tokens_per_req, context):
+        seen += min(p_ + 1, window) + (max(0, (p_ - window + 1) // pool) if kind == "pooled" else 0)
+    flops = 4.0 * hd * nq * seen * reqs
+    first = max(0, context - tokens_per_req - window + 1)
+    rows_read = (context - first) + (max(0, (context - window) // pool) if kind == "pooled" else 0)
+    nbytes = reqs * rows_read * nkv * hd * 2 * 2
+    return {"kernel": f"window_attention ({kind})", "requests": reqs, "tokens_per_request": tokens_per_req, "context": context,
+            "q_heads": nq, "kv_heads": nkv, "head_dim": hd, "window": window, "layers": layers, "us": round(ms * 1e3, 2),
+            "TFLOP/s": round(flops / ms / 1e9, 2), "GB/s": round(nbytes / ms / 1e6, 1)}
+
+
+def scan(tokens_per_req: int, reqs: int, inner: int, N: int, rank: int) -> dict:
+    """``selective_scan`` alone (step sizes and the chain in time).  Bytes: the state read and written, and per token
+    u (bfloat16), z, dt written and read, the output (bfloat16) and the projection row."""
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    T = tokens_per_req * reqs
+    u = torch.randn(T, inner, device=dev, dtype=torch.bfloat16)
+    proj = torch.randn(T, rank + 2 * N, device=dev)
+    z = torch.randn(T, inner, device=dev)
+    w_dt = torch.randn(rank, inner, device=dev) / rank ** 0.5
+    dt_b, D = torch.zeros(inner, device=dev), torch.ones(inner, device=dev)
+    A = -torch.exp(torch.rand(inner, N, device=dev))
+    layers = 1 if tokens_per_req > 1 else max(1, min(16, int(2e9 // (reqs * inner * N * 4))))
+    states = [torch.zeros(reqs, inner, N, device=dev) for _ in range(layers)]
+    out = torch.empty(T, inner, device=dev, dtype=torch.bfloat16)
+    starts = torch.arange(0, T + 1, tokens_per_req, dtype=torch.int32, device=dev)
+    slots = torch.arange(reqs, dtype=torch.int32, device=dev)
+
+    def all_layers():
+        for s in states:
+            k.selective_scan(u, proj, z, w_dt, dt_b, A, D, s, out, starts, slots, rank, N)
+    ms = (bk.timed_graph(all_layers, reps=1) if tokens_per_req == 1 else bk.timed(all_layers, n=5, warm=2)) / layers
+    nbytes = 2 * reqs * inner * N * 4 + T * (inner * (2 + 4 + 8 + 2) + (rank + 2 * N) * 4) + inner * (rank + N + 2) * 4
+    flops = T * inner * (2.0 * rank + 7.0 * N)
+    return {"kernel": "selective_scan (steps + chain)", "requests": reqs, "tokens_per_request": tokens_per_req, "inner": inner,
+            "state": N, "dt_rank": rank, "us": round(ms * 1e3, 2), "tokens/s": round(T / ms * 1e3, 1),
+            "GB/s": round(nbytes / ms / 1e6, 1), "fp32 TFLOP/s": round(flops / ms / 1e9, 2)}
+
+
+def run_tarulix(args) -> dict:
+    import bench
+    import bench_kernels as bk
+    from quanta_b200.config import MiniMaxM3Config, TarulixConfig
+    pk, pk_src = bench.peaks()
+    clocks = bench.ClockSampler()
+    clocks.start()
+    models = {}
+    for name, s in TARULIX_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        t0 = time.time()
+        t = _model_numbers(TarulixConfig.from_dict(tarulix_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        m = _model_numbers(MiniMaxM3Config.from_dict(minimax_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        models[name] = {"sizes": s, "tarulix": t, "minimax_m3": m}
+        print(f"[bench] {name}: tarulix {t}\n[bench] {name}: minimax_m3 {m} ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+    s = TARULIX_SIZES["w2048"]
+    T, B = args.prompt_len, args.batch
+    tensor, hbm = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    Hq, Hk, hd, W = s["attn_heads"], max(1, s["attn_heads"] // 4), s["dim"], s["window"]
+    ctx = 4 * T                                         # single tokens deep into a context: the window is full
+    wp = {kind: window_attn(T, 1, T, Hq, Hk, hd, W, kind, s["pool"]) for kind in ("biased", "pooled")}
+    wd = {kind: window_attn(1, B, ctx, Hq, Hk, hd, W, kind, s["pool"]) for kind in ("biased", "pooled")}
+    sp = bk.attn_span(T, 0, Hq, Hk, hd, 16)
+    sd = bk.attn_decode(B, W, Hq, Hk, hd, 16)           # as many keys as the window holds
+    for r in list(wp.values()) + [sp]:
+        r["frac_of_tensor_peak"] = round(r["TFLOP/s"] * 1e12 / tensor, 4)
+    for r in list(wd.values()) + [sd]:
+        r["frac_of_copy_bandwidth"] = round(r["GB/s"] * 1e9 / hbm, 4)
+    cp, cd = scan(T, 1, s["inner"], s["state"], s["dt_rank"]), scan(1, B, s["inner"], s["state"], s["dt_rank"])
+    gp, gd = gla(T, 1, 32, 64, 64), gla(1, B, 32, 64, 64)
+    for r in (cp, cd, gp, gd):
+        r["frac_of_copy_bandwidth"] = round(r["GB/s"] * 1e9 / hbm, 4)
+    kernels_alone = {"prompt_attention": {"tarulix": wp, "minimax_m3": sp}, "single_token_attention": {"tarulix": wd, "minimax_m3": sd},
+                     "recurrence_prompt": {"tarulix": cp, "tirizen_gla": gp}, "recurrence_single_tokens": {"tarulix": cd, "tirizen_gla": gd}}
+    for k_, v in kernels_alone.items():
+        print(f"[bench] {k_}: {v}", file=sys.stderr, flush=True)
+    first = next(iter(models.values()))["tarulix"] if models else {}
+    return {"metric": f"Tarulix decode tokens/s (batch {args.batch}, {args.prompt_len}-token prompts) beside MiniMax-M3 at equal sizes",
+            "value": first.get("decode_tok_s"), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": first.get("decode_ms"), "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic (seeded uniform token ids, seeded random weights)", "design": "tarulix", "models": models,
+            "kernels": kernels_alone, "peaks": {**pk, "source": pk_src}, "clocks": clocks.stop(),
+            "gpu_launches": first.get("launches_per_decode_step", 0) * args.steps, "impl": "ours"}
+
+
 def run(args) -> dict:
     if getattr(args, "design", "guravik") == "tirizen":
         return run_tirizen(args)
+    if getattr(args, "design", "guravik") == "tarulix":
+        return run_tarulix(args)
     import torch
     import bench
     import bench_kernels as bk
@@ -351,7 +515,10 @@ if __name__ == "__main__":
     # one kernel alone, one JSON line:  python bench_designs.py latent_prefill --tokens 1024
     import argparse
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["latent_prefill", "latent_decode", "delta_rule", "gla", "streams_norm"])
+    ap.add_argument("kernel", choices=["latent_prefill", "latent_decode", "delta_rule", "gla", "streams_norm", "window_prefill",
+                                       "window_decode", "scan"])
+    ap.add_argument("--kind", default="biased", choices=["biased", "pooled"])
+    ap.add_argument("--window", type=int, default=1024)
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--heads", type=int, default=16)
@@ -367,5 +534,11 @@ if __name__ == "__main__":
         print(json.dumps(gla(a.tokens, a.batch, a.heads, a.dim, a.dim)))
     elif a.kernel == "streams_norm":
         print(json.dumps(streams_norm(a.tokens, 3, 2048)))
+    elif a.kernel == "window_prefill":
+        print(json.dumps(window_attn(a.tokens, 1, a.tokens, a.heads, max(1, a.heads // 4), 128, a.window, a.kind)))
+    elif a.kernel == "window_decode":
+        print(json.dumps(window_attn(1, a.batch, a.tokens, a.heads, max(1, a.heads // 4), 128, a.window, a.kind)))
+    elif a.kernel == "scan":
+        print(json.dumps(scan(a.tokens, a.batch, 4096, 16, 128)))
     else:
         print(json.dumps(delta_rule(a.tokens, a.batch, a.heads, a.dim)))

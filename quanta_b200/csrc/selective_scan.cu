@@ -23,33 +23,43 @@ constexpr int SS_MAX_STATE = 256;
 
 __device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-// dt[t, c] for all tokens: a thread a (token, channel)
-__global__ void scan_steps_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ w_dt,
+// dt[t, c] for all tokens: a thread a (token, channel); w_dt is stored [R, inner], so the threads of a warp
+// (neighbouring channels of one token) read neighbouring numbers
+__global__ void scan_steps_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ w_dt_t,
                                   const float* __restrict__ dt_bias, float* __restrict__ dt, int T, int inner, int R) {
   const size_t n = (size_t)T * inner;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(i / inner), c = (int)(i % inner);
     const float* low = proj + (size_t)t * proj_stride;
-    const float* w = w_dt + (size_t)c * R;
     float acc = 0.f;
-    for (int r = 0; r < R; ++r) acc = fmaf(w[r], low[r], acc);
+    for (int r = 0; r < R; ++r) acc = fmaf(w_dt_t[(size_t)r * inner + c], low[r], acc);
     dt[i] = ss_softplus(acc + dt_bias[c]);
   }
 }
 
-// NPL: states a lane holds, N <= 8 * NPL
+// NPL: states a lane holds, N <= 8 * NPL.  The request's rows are walked in chunks of `tok` tokens: the block first
+// brings the chunk's step sizes, inputs and B / C vectors into shared memory (all threads, whole segments of the
+// rows), then every lane runs the chunk's steps from there (nothing in the chain waits for global memory), then
+// the block gates and writes the chunk's outputs.
 template <typename U, typename O, int NPL>
 __global__ void __launch_bounds__(SS_CH * SS_LANES)
 scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const float* __restrict__ proj,
                   int proj_stride, int b_off, int c_off, const float* __restrict__ z, int z_stride,
                   const float* __restrict__ A, const float* __restrict__ D, float* __restrict__ state,
                   O* __restrict__ out, const int* __restrict__ req_start, const int* __restrict__ req_slot, int inner,
-                  int N) {
+                  int N, int tok) {
+  extern __shared__ float ss_smem[];
+  float* s_dt = ss_smem;                        // [tok][SS_CH]
+  float* s_u = s_dt + tok * SS_CH;              // [tok][SS_CH]
+  float* s_y = s_u + tok * SS_CH;               // [tok][SS_CH]
+  float* s_B = s_y + tok * SS_CH;               // [tok][N]
+  float* s_C = s_B + tok * N;                   // [tok][N]
   const int r = blockIdx.y;
   const int first = req_start[r], last = req_start[r + 1];
   if (last <= first) return;
-  const int sub = threadIdx.x % SS_LANES;
-  const int c = blockIdx.x * SS_CH + threadIdx.x / SS_LANES;
+  const int sub = threadIdx.x % SS_LANES, ch = threadIdx.x / SS_LANES;
+  const int c0 = blockIdx.x * SS_CH;
+  const int c = c0 + ch;
   const bool live = c < inner;
   const int cc = live ? c : inner - 1;                       // idle lanes walk along (the shuffles want whole groups)
   float* Srow = state + ((size_t)req_slot[r] * inner + cc) * N;
@@ -61,28 +71,49 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const f
     a[i] = n < N ? A[(size_t)cc * N + n] : 0.f;
   }
   const float d_c = D[cc];
-  for (int t = first; t < last; ++t) {
-    const float dtv = dt[(size_t)t * inner + cc];
-    const float uv = qb_to_float<U>(u[(size_t)t * inner + cc]);
-    const float* Bt = proj + (size_t)t * proj_stride + b_off;
-    const float* Ct = proj + (size_t)t * proj_stride + c_off;
-    const float du = dtv * uv;
-    float y = 0.f;
+  for (int t0 = first; t0 < last; t0 += tok) {
+    const int nt = min(tok, last - t0);
+    for (int i = threadIdx.x; i < nt * SS_CH; i += blockDim.x) {
+      const int tt = i / SS_CH, k = min(c0 + i % SS_CH, inner - 1);
+      s_dt[i] = dt[(size_t)(t0 + tt) * inner + k];
+      s_u[i] = qb_to_float<U>(u[(size_t)(t0 + tt) * inner + k]);
+    }
+    for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
+      const int tt = i / N, n = i % N;
+      const float* row = proj + (size_t)(t0 + tt) * proj_stride;
+      s_B[i] = row[b_off + n];
+      s_C[i] = row[c_off + n];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float dtv = s_dt[tt * SS_CH + ch];
+      const float uv = s_u[tt * SS_CH + ch];
+      const float* Bt = s_B + tt * N;
+      const float* Ct = s_C + tt * N;
+      const float du = dtv * uv;
+      float y = 0.f;
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int n = sub + SS_LANES * i;
-      if (n < N) {
-        S[i] = fmaf(expf(dtv * a[i]), S[i], du * Bt[n]);
-        y = fmaf(S[i], Ct[n], y);
+      for (int i = 0; i < NPL; ++i) {
+        const int n = sub + SS_LANES * i;
+        if (n < N) {
+          S[i] = fmaf(expf(dtv * a[i]), S[i], du * Bt[n]);
+          y = fmaf(S[i], Ct[n], y);
+        }
+      }
+#pragma unroll
+      for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (sub == 0) s_y[tt * SS_CH + ch] = fmaf(d_c, uv, y);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * SS_CH; i += blockDim.x) {
+      const int tt = i / SS_CH, k = c0 + i % SS_CH;
+      if (k < inner) {
+        const float zv = z[(size_t)(t0 + tt) * z_stride + k];
+        out[(size_t)(t0 + tt) * inner + k] = qb_from_float<O>(s_y[i] * (zv / (1.f + expf(-zv))));
       }
     }
-#pragma unroll
-    for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-    if (sub == 0 && live) {
-      y = fmaf(d_c, uv, y);
-      const float zv = z[(size_t)t * z_stride + c];
-      out[(size_t)t * inner + c] = qb_from_float<O>(y * (zv / (1.f + expf(-zv))));
-    }
+    // the next chunk's loads write s_dt / s_u / s_B / s_C, which no thread reads any more, and s_y only after the
+    // barrier that follows them
   }
   if (live) {
 #pragma unroll
@@ -94,7 +125,7 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const f
 }
 
 // u [T, inner] in the activation dtype; proj float32 rows [low (R) | B (N) | C (N) | ...]; z float32 rows of
-// z_stride; w_dt float32 [inner, R]; A float32 [inner, N] (already -exp(A_log)); state float32 [slots, inner, N];
+// z_stride; w_dt_t float32 [R, inner] (the step projection, transposed); A float32 [inner, N] (already -exp(A_log)); state float32 [slots, inner, N];
 // dt float32 scratch [T, inner]; out [T, inner] in the activation dtype.
 extern "C" int qb_selective_scan(const void* u, int dtype, const float* proj, int proj_stride, const float* z,
                                  int z_stride, const float* w_dt, const float* dt_bias, const float* A, const float* D,
@@ -108,9 +139,16 @@ extern "C" int qb_selective_scan(const void* u, int dtype, const float* proj, in
   scan_steps_kernel<<<blocks, 256, 0, stream>>>(proj, proj_stride, w_dt, dt_bias, dt, T, inner, rank);
   QB_LAUNCH_CHECK();
   dim3 grid((inner + SS_CH - 1) / SS_CH, R_req);
+  // tokens a chunk: at most 32, at most the longest portion can be, and what 44 KB of shared memory hold
+  const int per_tok = (3 * SS_CH + 2 * N) * (int)sizeof(float);
+  int tok = 44 * 1024 / per_tok;
+  tok = tok > 32 ? 32 : tok;
+  tok = tok > T ? T : tok;
+  const size_t smem = (size_t)tok * per_tok;
 #define QB_SS_LAUNCH(NPL)                                                                                             \
-  QB_DISPATCH_DTYPE(dtype, U, (scan_chain_kernel<U, U, NPL><<<grid, SS_CH * SS_LANES, 0, stream>>>(                   \
-      (const U*)u, dt, proj, proj_stride, rank, rank + N, z, z_stride, A, D, state, (U*)out, req_start, req_slot, inner, N)))
+  QB_DISPATCH_DTYPE(dtype, U, (scan_chain_kernel<U, U, NPL><<<grid, SS_CH * SS_LANES, smem, stream>>>(                \
+      (const U*)u, dt, proj, proj_stride, rank, rank + N, z, z_stride, A, D, state, (U*)out, req_start, req_slot, inner, N, \
+      tok)))
   if (N <= 8 * 2) QB_SS_LAUNCH(2);
   else if (N <= 8 * 4) QB_SS_LAUNCH(4);
   else if (N <= 8 * 8) QB_SS_LAUNCH(8);

@@ -16,7 +16,9 @@
 // computed as out_h = sum_g talk[h, g] O[g][kv(h)] with O[g][m] = sum_j w_g(j) v_m(j): every head's weights are
 // applied to the values of ALL kv heads (float32 scratch [T, nq, nkv, vd]) and a second kernel mixes.
 //
-// One warp per (token, q head): lanes own keys for the scores, then own dims for P V.
+// One warp per (token, q head), or per (token, q head, range of the keys) in steps of few tokens, whose ranges a
+// second kernel joins: lanes own keys for the scores, then own dims for P V.  Long portions in bfloat16 take the
+// tensor-core kernel at the end of this file.
 #include "common.cuh"
 
 constexpr int WA_WARPS = 4;
@@ -57,6 +59,8 @@ struct WaParams {
   const float* sink;           // [nq] or null
   int all_values;              // 1: every head's weights on the values of all kv heads (scratch), 0: its own
   int vec;
+  int n_split;                 // > 1: a warp takes one of n_split ranges of the keys and leaves (max, sum, sums of
+  float* part;                 // values) in `part` [T, nq, n_split, 2 + (all_values ? nkv : 1) * vd] for the merge
   int* status;
 };
 
@@ -69,8 +73,9 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
   extern __shared__ float wa_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long wid = (long)blockIdx.x * WA_WARPS + warp;
-  if (wid >= (long)P.T * P.nq) return;
-  const int t = (int)(wid / P.nq), h = (int)(wid % P.nq);
+  if (wid >= (long)P.T * P.nq * P.n_split) return;
+  const int split = (int)(wid % P.n_split);
+  const int t = (int)(wid / P.n_split / P.nq), h = (int)(wid / P.n_split % P.nq);
   const int nq = P.nq, nkv = P.nkv, hd = P.hd, vd = P.vd, ps = P.page_size;
   const int kvh = h / (nq / nkv);
   const int GV = P.all_values ? nkv : 1;
@@ -90,18 +95,22 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
   // pooled blocks that lie wholly before the window: b * pool + pool - 1 <= pos - window
   const int n_blocks = (pt != nullptr && P.window > 0 && pos - P.window + 1 >= P.pool) ? (pos - P.window + 1) / P.pool : 0;
   const int n_keys = n_blocks + (pos - lo + 1);
+  // this warp's range of the keys: whole rounds of 32
+  const int per_split = ((n_keys + P.n_split - 1) / P.n_split + 31) / 32 * 32;
+  const int k_begin = split * per_split;
+  const int k_end = min(n_keys, k_begin + per_split);
 
   float m = -INFINITY, l = 0.f;
   float acc[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) acc[i] = 0.f;
 
-  for (int k0 = 0; k0 < n_keys; k0 += 32) {
+  for (int k0 = k_begin; k0 < k_end; k0 += 32) {
     const int idx = k0 + lane;
     float s = -INFINITY;
     long base = -1;       // row of this lane's key among all (page, kv head 0, slot) rows; + m * page_size for kv head m
     int pooled = 0;
-    if (idx < n_keys) {
+    if (idx < k_end) {
       pooled = idx < n_blocks;
       const int row = pooled ? idx : lo + (idx - n_blocks);       // pooled row or token position
       const int page = pooled ? pt[row / ps] : bt[row / ps];
@@ -133,7 +142,7 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
     const float corr = expf(m - m_new);
     l = l * corr + qb_warp_sum(p);
     m = m_new;
-    const int n_here = min(32, n_keys - k0);
+    const int n_here = min(32, k_end - k0);
     for (int g = 0; g < GV; ++g) {
       const int vh = P.all_values ? g : kvh;
       if (P.all_values) {
@@ -166,6 +175,20 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
       }
     }
   }
+  if (P.n_split > 1) {
+    float* prow = P.part + (size_t)wid * (2 + GV * vd);
+    if (lane == 0) { prow[0] = m; prow[1] = l; }
+    if (P.all_values) {
+      for (int i = lane; i < nkv * vd; i += 32) prow[2 + i] = acc_sm[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int d = lane + 32 * i;
+        if (d < vd) prow[2 + d] = acc[i];
+      }
+    }
+    return;
+  }
   float denom = l;
   if (P.sink != nullptr) denom += (m == -INFINITY) ? 1.f : expf(P.sink[h] - m);
   const float inv_l = denom > 0.f ? 1.f / denom : 0.f;
@@ -179,6 +202,45 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
       const int d = lane + 32 * i;
       if (d < vd) orow[d] = qb_from_float<A>(acc[i] * inv_l);
     }
+  }
+}
+
+// The ranges of a (token, head) joined: with M = max of the ranges' maxima, weight_r = exp(m_r - M) / (sum_r l_r
+// exp(m_r - M) + exp(sink - M)); the normed sums of values go to `out` (own kv head) or, when the heads' weights
+// are mixed afterwards, to scratch [T, nq, nkv, vd].  One block per token; its shared memory holds the weights
+// [nq, n_split].
+template <typename A>
+__global__ void wa_merge_kernel(const float* __restrict__ part, const float* __restrict__ sink, A* __restrict__ out,
+                                float* __restrict__ scratch, int T, int nq, int nkv, int vd, int n_split, int all_values) {
+  extern __shared__ float wm_w[];
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  const int GV = all_values ? nkv : 1;
+  const size_t stride = 2 + (size_t)GV * vd;
+  const float* prow = part + (size_t)t * nq * n_split * stride;
+  for (int h = threadIdx.x; h < nq; h += blockDim.x) {
+    float M = -INFINITY;
+    for (int r = 0; r < n_split; ++r) M = fmaxf(M, prow[((size_t)h * n_split + r) * stride]);
+    float denom = 0.f;
+    for (int r = 0; r < n_split; ++r) {
+      const float* pr = prow + ((size_t)h * n_split + r) * stride;
+      const float e = pr[0] == -INFINITY ? 0.f : expf(pr[0] - M);
+      wm_w[h * n_split + r] = e;
+      denom += pr[1] * e;
+    }
+    if (sink != nullptr) denom += (M == -INFINITY) ? 1.f : expf(sink[h] - M);
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    for (int r = 0; r < n_split; ++r) wm_w[h * n_split + r] *= inv;
+  }
+  __syncthreads();
+  const int n = nq * GV * vd;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int h = i / (GV * vd), rest = i % (GV * vd);
+    float v = 0.f;
+    for (int r = 0; r < n_split; ++r)
+      v = fmaf(wm_w[h * n_split + r], prow[((size_t)h * n_split + r) * stride + 2 + rest], v);
+    if (all_values) scratch[(size_t)t * n + i] = v;
+    else out[(size_t)t * n + i] = qb_from_float<A>(v);
   }
 }
 
@@ -204,8 +266,9 @@ extern "C" int qb_window_attention(const void* q, int dtype, const void* k_cache
                                    int bt_stride, const int* pool_table, int pool_stride, int T, int nq, int nkv,
                                    int hd, int vd, int page_size, int num_pages, int num_pool_pages, float scale,
                                    float cap, int window, int pool, const float* dist_bias, const float* sink,
-                                   int* status, cudaStream_t stream) {
+                                   float* part, int n_split, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (n_split < 1 || (n_split > 1 && part == nullptr)) return QB_ERR_BAD_ARG;
   if (hd <= 0 || vd <= 0 || hd > WA_MAX_HD || vd > WA_MAX_HD || nq % nkv || page_size <= 0) return QB_ERR_UNSUPPORTED;
   if (pool_table != nullptr && (pool <= 0 || window <= 0 || kp_cache == nullptr || vp_cache == nullptr)) return QB_ERR_BAD_ARG;
   if (dist_bias != nullptr && window <= 0) return QB_ERR_BAD_ARG;
@@ -217,7 +280,8 @@ extern "C" int qb_window_attention(const void* q, int dtype, const void* k_cache
   P.num_pool_pages = num_pool_pages; P.scale = scale; P.cap = cap; P.window = window; P.pool = pool;
   P.dist_bias = dist_bias; P.sink = sink; P.all_values = talk != nullptr; P.status = status;
   P.vec = (hd % 8 == 0 && ((uintptr_t)k_cache & 15) == 0 && (kp_cache == nullptr || ((uintptr_t)kp_cache & 15) == 0)) ? 1 : 0;
-  const long warps = (long)T * nq;
+  P.n_split = n_split; P.part = part;
+  const long warps = (long)T * nq * n_split;
   const int blocks = (int)((warps + WA_WARPS - 1) / WA_WARPS);
   const size_t smem = (size_t)WA_WARPS * (hd + (P.all_values ? nkv * vd : 0)) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
@@ -240,6 +304,13 @@ extern "C" int qb_window_attention(const void* q, int dtype, const void* k_cache
   });
 #undef QB_WA_LAUNCH
   QB_LAUNCH_CHECK();
+  if (n_split > 1) {
+    const size_t wsm = (size_t)nq * n_split * sizeof(float);
+    if (wsm > 48 * 1024) return QB_ERR_UNSUPPORTED;
+    QB_DISPATCH_DTYPE(dtype, A, wa_merge_kernel<A><<<T, 256, wsm, stream>>>(part, sink, (A*)out, scratch, T, nq, nkv, vd,
+                                                                           n_split, P.all_values));
+    QB_LAUNCH_CHECK();
+  }
   if (talk != nullptr) {
     QB_DISPATCH_DTYPE(dtype, A, talk_mix_kernel<A><<<T, 256, 0, stream>>>(scratch, talk, (A*)out, T, nq, nkv, vd));
     QB_LAUNCH_CHECK();
@@ -298,5 +369,302 @@ extern "C" int qb_pool_blocks(const void* k_cache, const void* v_cache, void* kp
       (const A*)k_cache, (const A*)v_cache, (A*)kp_cache, (A*)vp_cache, tok_pos, tok_req, block_table, bt_stride,
       pool_table, pool_stride, T, nkv, hd, vd, page_size, num_pages, num_pool_pages, pool, status));
   QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-core version for prompt portions (bfloat16 q and caches; head sizes that are multiples of 16, values of
+// at most 128 a head).  A block owns 64 rows of the step's token list for one q head (four warps of 16 rows) and
+// walks the keys in tiles of 64: S = Q K^T with mma.sync m16n8k16 (float32 accumulators), then scale, cap, bias
+// and the mask per element in float32, the running maximum and sum per row, and O += P V with P split in two
+// bfloat16 parts (p = hi + lo, two MMAs), so that the weights enter the sum with 16 bits of mantissa and not 8.
+// The rows of a tile may belong to several requests: the keys are walked request by request (the step's tokens
+// of a request are neighbours), rows of other requests are masked, warps without a row of the request idle.
+// With mixed heads every (q head g, kv head m) pair is a block of its own that applies g's weights to m's values
+// and leaves the normed sums in scratch [T, nq, nkv, vd] for the mixing kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int WM_BM = 64, WM_BN = 64;
+
+__device__ __forceinline__ void wm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void wm_ldmatrix_x2(uint32_t (&r)[2], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void wm_ldmatrix_x2_trans(uint32_t (&r)[2], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void wm_mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// two floats -> their bfloat16 roundings (hi) and the roundings of what is left (lo), each packed low | high
+__device__ __forceinline__ void wm_split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+  const __nv_bfloat16 xl = __float2bfloat16_rn(x - __bfloat162float(xh)), yl = __float2bfloat16_rn(y - __bfloat162float(yh));
+  hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
+  lo = (uint32_t)__bfloat16_as_ushort(xl) | ((uint32_t)__bfloat16_as_ushort(yl) << 16);
+}
+
+// NTV: value tiles of 8 a warp accumulates, vd <= 8 * NTV
+template <int NTV>
+__global__ void __launch_bounds__(128)
+window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                            const __nv_bfloat16* __restrict__ v_cache, const __nv_bfloat16* __restrict__ kp_cache,
+                            const __nv_bfloat16* __restrict__ vp_cache, __nv_bfloat16* __restrict__ out,
+                            float* __restrict__ scratch, const WaParams P) {
+  extern __shared__ __align__(16) unsigned char wm_smem[];
+  const int hd = P.hd, vd = P.vd, nq = P.nq, nkv = P.nkv, ps = P.page_size;
+  const int pq = hd + 8, pv = vd + 8;                                  // row pitches in elements (16-byte multiples)
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);      // [64][pq]
+  __nv_bfloat16* Ks = Qs + WM_BM * pq;                                 // [64][pq]
+  __nv_bfloat16* Vs = Ks + WM_BN * pq;                                 // [64][pv]
+  int* s_pos = reinterpret_cast<int*>(Vs + WM_BN * pv);                // [64]
+  int* s_req = s_pos + WM_BM;                                          // [64]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int t0 = blockIdx.x * WM_BM;
+  const int h = blockIdx.y;
+  const int kvh_k = h / (nq / nkv);
+  const int kvh_v = P.all_values ? (int)blockIdx.z : kvh_k;
+  const int n_rows = min(WM_BM, P.T - t0);
+  const int qc = hd / 8, vc = vd / 8;                                  // 16-byte pieces a row
+
+  for (int i = tid; i < WM_BM; i += 128) {
+    s_pos[i] = i < n_rows ? P.tok_pos[t0 + i] : 0;
+    s_req[i] = i < n_rows ? P.tok_req[t0 + i] : -1;
+  }
+  for (int i = tid; i < WM_BM * qc; i += 128) {
+    const int r = i / qc, c = i % qc;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < n_rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r) * nq + h) * hd + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * pq + c * 8) = v;
+  }
+  __syncthreads();
+
+  // this thread's two rows: warp * 16 + g8 and + 8
+  const int r_a = warp * 16 + g8, r_b = r_a + 8;
+  const int pos_a = s_pos[r_a], pos_b = s_pos[r_b];
+  const int req_a = s_req[r_a], req_b = s_req[r_b];
+  const int lo_a = (P.window > 0 && pos_a - P.window + 1 > 0) ? pos_a - P.window + 1 : 0;
+  const int lo_b = (P.window > 0 && pos_b - P.window + 1 > 0) ? pos_b - P.window + 1 : 0;
+  const bool pooling = P.pool_table != nullptr && P.window > 0;
+  const int nb_a = (pooling && pos_a - P.window + 1 >= P.pool) ? (pos_a - P.window + 1) / P.pool : 0;
+  const int nb_b = (pooling && pos_b - P.window + 1 >= P.pool) ? (pos_b - P.window + 1) / P.pool : 0;
+
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  float o[NTV][4];
+#pragma unroll
+  for (int i = 0; i < NTV; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+  int ra = 0;
+  while (ra < n_rows) {
+    const int req = s_req[ra];
+    int rb = ra + 1;
+    while (rb < n_rows && s_req[rb] == req) ++rb;
+    // the keys that any row of the request's rows [ra, rb) reads
+    int lo_min = 0x7fffffff, pos_max = -1, nb_max = 0;
+    for (int r = ra; r < rb; ++r) {
+      const int p = s_pos[r];
+      const int lo = (P.window > 0 && p - P.window + 1 > 0) ? p - P.window + 1 : 0;
+      const int nb = (pooling && p - P.window + 1 >= P.pool) ? (p - P.window + 1) / P.pool : 0;
+      lo_min = min(lo_min, lo); pos_max = max(pos_max, p); nb_max = max(nb_max, nb);
+    }
+    const int n_keys = nb_max + (pos_max - lo_min + 1);
+    const bool warp_active = warp * 16 < rb && warp * 16 + 16 > ra;
+    const bool mine_a = req_a == req && r_a >= ra && r_a < rb, mine_b = req_b == req && r_b >= ra && r_b < rb;
+    const int* bt = P.block_table + (size_t)req * P.bt_stride;
+    const int* pt = pooling ? P.pool_table + (size_t)req * P.pool_stride : nullptr;
+
+    for (int k0 = 0; k0 < n_keys; k0 += WM_BN) {
+      __syncthreads();                                                 // the last tile has been read by all warps
+      for (int i = tid; i < WM_BN * (qc + vc); i += 128) {
+        const bool is_k = i < WM_BN * qc;
+        const int j = is_k ? i : i - WM_BN * qc;
+        const int w = is_k ? qc : vc;
+        const int r = j / w, c = j % w;
+        const int idx = k0 + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (idx < n_keys) {
+          const bool pooled = idx < nb_max;
+          const int row = pooled ? idx : lo_min + (idx - nb_max);
+          const int page = pooled ? pt[row / ps] : bt[row / ps];
+          if (page < 0 || page >= (pooled ? P.num_pool_pages : P.num_pages)) {
+            qb_set_status(P.status, QB_STATUS_BAD_PAGE, page, 3);
+          } else {
+            const size_t base = ((size_t)page * nkv) * ps + row % ps;
+            if (is_k) v = *reinterpret_cast<const uint4*>((pooled ? kp_cache : k_cache) + (base + (size_t)kvh_k * ps) * hd + c * 8);
+            else v = *reinterpret_cast<const uint4*>((pooled ? vp_cache : v_cache) + (base + (size_t)kvh_v * ps) * vd + c * 8);
+          }
+        }
+        if (is_k) *reinterpret_cast<uint4*>(Ks + r * pq + c * 8) = v;
+        else *reinterpret_cast<uint4*>(Vs + r * pv + c * 8) = v;
+      }
+      __syncthreads();
+      if (!warp_active) continue;
+
+      float s[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+      for (int kk = 0; kk < hd; kk += 16) {
+        uint32_t a[4];
+        wm_ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * pq + kk + (lane >> 4) * 8);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          uint32_t b[2];
+          wm_ldmatrix_x2(b, Ks + (nt * 8 + (lane & 7)) * pq + kk + ((lane >> 3) & 1) * 8);
+          wm_mma(s[nt], a, b);
+        }
+      }
+      // scale, cap, bias, mask
+      float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const bool second = e >= 2;
+          const int idx = k0 + nt * 8 + 2 * t4 + (e & 1);
+          const bool mine = second ? mine_b : mine_a;
+          const int pos = second ? pos_b : pos_a;
+          float x = -INFINITY;
+          if (mine && idx < n_keys) {
+            if (idx < nb_max) {
+              if (idx < (second ? nb_b : nb_a)) {
+                x = s[nt][e] * P.scale;
+                if (P.cap > 0.f) x = P.cap * tanhf(x / P.cap);
+              }
+            } else {
+              const int j = lo_min + (idx - nb_max);
+              if (j >= (second ? lo_b : lo_a) && j <= pos) {
+                x = s[nt][e] * P.scale;
+                if (P.cap > 0.f) x = P.cap * tanhf(x / P.cap);
+                if (P.dist_bias != nullptr) x += __ldg(P.dist_bias + (size_t)(pos - j) * nq + h);
+              }
+            }
+          }
+          s[nt][e] = x;
+          if (second) mx_b = fmaxf(mx_b, x); else mx_a = fmaxf(mx_a, x);
+        }
+      }
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      if (!__any_sync(0xffffffffu, mx_a > -INFINITY || mx_b > -INFINITY)) continue;     // no row of the warp sees the tile
+      const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+      const float corr_a = mn_a == -INFINITY ? 1.f : expf(m_a - mn_a), corr_b = mn_b == -INFINITY ? 1.f : expf(m_b - mn_b);
+      m_a = mn_a; m_b = mn_b;
+      float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        s[nt][0] = s[nt][0] == -INFINITY ? 0.f : expf(s[nt][0] - mn_a);
+        s[nt][1] = s[nt][1] == -INFINITY ? 0.f : expf(s[nt][1] - mn_a);
+        s[nt][2] = s[nt][2] == -INFINITY ? 0.f : expf(s[nt][2] - mn_b);
+        s[nt][3] = s[nt][3] == -INFINITY ? 0.f : expf(s[nt][3] - mn_b);
+        sum_a += s[nt][0] + s[nt][1];
+        sum_b += s[nt][2] + s[nt][3];
+      }
+      l_a = l_a * corr_a + sum_a;
+      l_b = l_b * corr_b + sum_b;
+#pragma unroll
+      for (int i = 0; i < NTV; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t ah[4], al[4];
+        wm_split_pair(s[2 * ks][0], s[2 * ks][1], ah[0], al[0]);
+        wm_split_pair(s[2 * ks][2], s[2 * ks][3], ah[1], al[1]);
+        wm_split_pair(s[2 * ks + 1][0], s[2 * ks + 1][1], ah[2], al[2]);
+        wm_split_pair(s[2 * ks + 1][2], s[2 * ks + 1][3], ah[3], al[3]);
+#pragma unroll
+        for (int nt = 0; nt < NTV; ++nt) {
+          if (nt * 8 < vd) {
+            uint32_t b[2];
+            wm_ldmatrix_x2_trans(b, Vs + (ks * 16 + (lane & 15)) * pv + nt * 8);
+            wm_mma(o[nt], ah, b);
+            wm_mma(o[nt], al, b);
+          }
+        }
+      }
+    }
+    ra = rb;
+  }
+
+  // the rows' sums over the four lanes that share them, the sink, and the division
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  if (P.sink != nullptr) {
+    l_a += m_a == -INFINITY ? 1.f : expf(P.sink[h] - m_a);
+    l_b += m_b == -INFINITY ? 1.f : expf(P.sink[h] - m_b);
+  }
+  const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+#pragma unroll
+  for (int nt = 0; nt < NTV; ++nt) {
+    const int d = nt * 8 + 2 * t4;
+    if (d >= vd) continue;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = half ? r_b : r_a;
+      if (r >= n_rows) continue;
+      const float x = o[nt][2 * half] * (half ? inv_b : inv_a), y = o[nt][2 * half + 1] * (half ? inv_b : inv_a);
+      if (P.all_values) {
+        float* dst = scratch + (((size_t)(t0 + r) * nq + h) * nkv + kvh_v) * vd + d;
+        dst[0] = x; dst[1] = y;
+      } else {
+        __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nq + h) * vd + d;
+        dst[0] = __float2bfloat16_rn(x); dst[1] = __float2bfloat16_rn(y);
+      }
+    }
+  }
+}
+
+extern "C" int qb_window_attention_mma_supported(int dtype, int hd, int vd) {
+  return dtype == QB_BF16 && hd > 0 && hd <= WA_MAX_HD && hd % 16 == 0 && vd > 0 && vd <= 128 && vd % 16 == 0;
+}
+
+extern "C" int qb_window_attention_mma(const void* q, int dtype, const void* k_cache, const void* v_cache,
+                                       const void* kp_cache, const void* vp_cache, void* out, float* scratch,
+                                       const float* talk, const int* tok_pos, const int* tok_req, const int* block_table,
+                                       int bt_stride, const int* pool_table, int pool_stride, int T, int nq, int nkv,
+                                       int hd, int vd, int page_size, int num_pages, int num_pool_pages, float scale,
+                                       float cap, int window, int pool, const float* dist_bias, const float* sink,
+                                       int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (!qb_window_attention_mma_supported(dtype, hd, vd) || nq % nkv || page_size <= 0 || nq > 65535 || nkv > 65535)
+    return QB_ERR_UNSUPPORTED;
+  if (pool_table != nullptr && (pool <= 0 || window <= 0 || kp_cache == nullptr || vp_cache == nullptr)) return QB_ERR_BAD_ARG;
+  if (dist_bias != nullptr && window <= 0) return QB_ERR_BAD_ARG;
+  if (talk != nullptr && scratch == nullptr) return QB_ERR_BAD_ARG;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)kp_cache | (uintptr_t)vp_cache) & 15) return QB_ERR_BAD_ARG;
+  WaParams P;
+  P.tok_pos = tok_pos; P.tok_req = tok_req; P.block_table = block_table; P.bt_stride = bt_stride;
+  P.pool_table = pool_table; P.pool_stride = pool_stride;
+  P.T = T; P.nq = nq; P.nkv = nkv; P.hd = hd; P.vd = vd; P.page_size = page_size; P.num_pages = num_pages;
+  P.num_pool_pages = num_pool_pages; P.scale = scale; P.cap = cap; P.window = window; P.pool = pool;
+  P.dist_bias = dist_bias; P.sink = sink; P.all_values = talk != nullptr; P.status = status; P.vec = 1;
+  P.n_split = 1; P.part = nullptr;
+  const size_t smem = ((size_t)(WM_BM + WM_BN) * (hd + 8) + (size_t)WM_BN * (vd + 8)) * 2 + 2 * WM_BM * sizeof(int);
+  dim3 grid((T + WM_BM - 1) / WM_BM, nq, P.all_values ? nkv : 1);
+#define QB_WM_LAUNCH(NTV)                                                                                         \
+  do {                                                                                                            \
+    auto kern = window_attention_mma_kernel<NTV>;                                                                 \
+    if (smem > 48 * 1024) {                                                                                       \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+      if (e != cudaSuccess) return (int)e;                                                                        \
+    }                                                                                                             \
+    kern<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,                     \
+                                      (const __nv_bfloat16*)v_cache, (const __nv_bfloat16*)kp_cache,              \
+                                      (const __nv_bfloat16*)vp_cache, (__nv_bfloat16*)out, scratch, P);           \
+  } while (0)
+  if (vd <= 64) QB_WM_LAUNCH(8);
+  else QB_WM_LAUNCH(16);
+#undef QB_WM_LAUNCH
+  QB_LAUNCH_CHECK();
+  if (talk != nullptr) {
+    talk_mix_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(scratch, talk, (__nv_bfloat16*)out, T, nq, nkv, vd);
+    QB_LAUNCH_CHECK();
+  }
   return 0;
 }

@@ -835,15 +835,27 @@ def latent_attend(q_lat, q_rot, cache, sink, out, tok_pos, tok_req, block_table,
 
 
 # ---- sliding-window attention with extras (csrc/window_attention.cu) ---------------------------------------------
+def window_attention_uses_tensor_cores(dtype, hd: int, vd: int) -> bool:
+    """Whether ``window_attention`` can run these shapes on the tensor cores (bfloat16, key sizes that are multiples
+    of 16 up to 256, value sizes that are multiples of 16 up to 128)."""
+    return dtype == torch.bfloat16 and bool(lib().qb_window_attention_mma_supported(BF16, int(hd), int(vd)))
+
+
 def window_attention(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, scale: float, window: int, status, *,
                      dist_bias=None, sink=None, softcap: float = 0.0, pool: int = 0, pooled_k=None, pooled_v=None,
-                     pool_table=None, talk=None, scratch=None) -> None:
+                     pool_table=None, talk=None, scratch=None, n_split: int | None = None, n_requests: int | None = None,
+                     tensor_cores: bool | None = None) -> None:
     """Softmax attention of every token over the last ``window`` keys of its request (0: all of them).  Options:
     ``dist_bias`` float32 ``[window, heads]`` added to the score by distance; ``sink`` float32 ``[heads]``, a term
     ``exp(sink)`` of the denominator; ``softcap`` c > 0: ``score <- c tanh(score / c)``; ``pool`` P with the pooled
     pages and their block table: one more key and value per block of P tokens that lies wholly before the window;
     ``talk`` float32 ``[heads, heads]``: the heads' softmax weights are mixed, ``w'_h = sum_g talk[h, g] w_g``
-    (``scratch`` float32 ``[T, heads, kv heads, vd]``).  float32 arithmetic; q, caches and out in one dtype."""
+    (``scratch`` float32 ``[T, heads, kv heads, vd]``).  float32 arithmetic; q, caches and out in one dtype.
+    A step of few tokens (single tokens of a few requests) cuts every token's keys into ``n_split`` ranges that
+    run as warps of their own and are joined by a second launch (None: chosen from the step's size).
+    A step with long portions (``n_requests`` given, at least 32 tokens and 8 a request on average) of shapes that
+    ``window_attention_uses_tensor_cores`` takes runs scores and sums on the tensor cores; ``tensor_cores`` True
+    forces that path (and raises where it cannot run), False keeps the CUDA cores."""
     T, nq, hd = q.shape
     num_pages, nkv, page_size, hd2 = k_cache.shape
     vd = v_cache.shape[3]
@@ -868,12 +880,31 @@ def window_attention(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, sc
         _want(talk, torch.float32, "talk"); _want(scratch, torch.float32, "scratch")
         if tuple(talk.shape) != (nq, nq) or scratch.numel() < T * nq * nkv * vd:
             raise ValueError("window_attention: talk must be [heads, heads] and scratch [T, heads, kv heads, vd]")
+    mma = tensor_cores is not False and window_attention_uses_tensor_cores(q.dtype, hd, vd) and (
+        tensor_cores or (n_requests is not None and T >= 32 and T >= 8 * n_requests))
+    if tensor_cores and not mma:
+        raise ValueError("window_attention: these shapes or dtypes do not run on the tensor cores")
+    if mma:
+        _check(lib().qb_window_attention_mma(
+            _p(q), _code(q), _p(k_cache), _p(v_cache), _p(pooled_k), _p(pooled_v), _p(out), _p(scratch), _p(talk),
+            _p(tok_pos), _p(tok_req), _p(block_table), block_table.shape[1], _p(pool_table),
+            pool_table.shape[1] if pool_table is not None else 0, T, nq, nkv, hd, vd, page_size, num_pages, n_pool_pages,
+            ctypes.c_float(scale), ctypes.c_float(softcap), int(window), int(pool), _p(dist_bias), _p(sink), _p(status),
+            _stream()), "window_attention_mma", 1 + (talk is not None))
+        return
+    if n_split is None:
+        warps = T * nq
+        n_split = 1 if (warps >= 1024 or window <= 0) else max(1, min(-(-2048 // warps), -(-window // 64), 64))
+    part = None
+    if n_split > 1:
+        part = torch.empty(T * nq * n_split * (2 + (nkv if talk is not None else 1) * vd), dtype=torch.float32,
+                           device=q.device)
     _check(lib().qb_window_attention(
         _p(q), _code(q), _p(k_cache), _p(v_cache), _p(pooled_k), _p(pooled_v), _p(out), _p(scratch), _p(talk),
         _p(tok_pos), _p(tok_req), _p(block_table), block_table.shape[1], _p(pool_table),
         pool_table.shape[1] if pool_table is not None else 0, T, nq, nkv, hd, vd, page_size, num_pages, n_pool_pages,
-        ctypes.c_float(scale), ctypes.c_float(softcap), int(window), int(pool), _p(dist_bias), _p(sink), _p(status),
-        _stream()), "window_attention", 2 if talk is not None else 1)
+        ctypes.c_float(scale), ctypes.c_float(softcap), int(window), int(pool), _p(dist_bias), _p(sink), _p(part),
+        int(n_split), _p(status), _stream()), "window_attention", 1 + (talk is not None) + (n_split > 1))
 
 
 def pool_blocks(k_cache, v_cache, pooled_k, pooled_v, tok_pos, tok_req, block_table, pool_table, pool: int, status) -> None:
@@ -898,13 +929,13 @@ def selective_scan(u, proj, z, w_dt, dt_bias, A, D, state, out, req_start, req_s
     """``S <- exp(dt A) S + dt u B``, ``y = S C + D u``, ``out = y * silu(z)`` per channel over each request's rows, with
     ``dt = softplus(w_dt low + dt_bias)``.  ``u`` ``[T, inner]`` in the activation dtype; ``proj`` float32 rows
     ``[low (rank) | B (n_state) | C (n_state)]``; ``z`` float32 ``[T, inner]`` (a column range of wider rows is fine);
-    ``w_dt`` float32 ``[inner, rank]``; ``A`` float32 ``[inner, n_state]`` (negative); ``state`` float32
+    ``w_dt`` float32 ``[rank, inner]`` (the step projection, transposed); ``A`` float32 ``[inner, n_state]`` (negative); ``state`` float32
     ``[slots, inner, n_state]``, read and left updated at the rows ``req_slot``."""
     T, inner = u.shape
     for t, n in ((proj, "proj"), (z, "z"), (w_dt, "w_dt"), (dt_bias, "dt_bias"), (A, "A"), (D, "D"), (state, "state")):
         _want(t, torch.float32, n)
     if (proj.shape[0] != T or proj.shape[1] < rank + 2 * n_state or proj.stride(1) != 1 or tuple(z.shape) != (T, inner)
-            or z.stride(1) != 1 or tuple(w_dt.shape) != (inner, rank) or tuple(A.shape) != (inner, n_state)
+            or z.stride(1) != 1 or tuple(w_dt.shape) != (rank, inner) or tuple(A.shape) != (inner, n_state)
             or D.numel() != inner or dt_bias.numel() != inner or tuple(state.shape[1:]) != (inner, n_state)
             or tuple(out.shape) != (T, inner) or out.dtype != u.dtype):
         raise ValueError("selective_scan: shape mismatch")

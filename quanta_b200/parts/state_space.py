@@ -56,7 +56,7 @@ class SelectiveScan(Mixer):
         rows = -(-w_x.shape[0] // 8) * 8               # product rows that start on 16 bytes
         self.w_x = torch.zeros((rows, self.inner), dtype=w_x.dtype, device=w_x.device)
         self.w_x[: w_x.shape[0]].copy_(w_x)
-        self.w_dt, self.dt_b = fetch(n["dt"]).contiguous(), fetch(n["dt_b"]).contiguous()
+        self.w_dt, self.dt_b = fetch(n["dt"]).t().contiguous(), fetch(n["dt_b"]).contiguous()    # [dt_rank, inner]
         self.A = (-torch.exp(fetch(n["A_log"]).float())).contiguous()
         self.D, self.w_o = fetch(n["D"]).contiguous(), fetch(n["o"])
 

@@ -176,6 +176,7 @@ class WindowAttention(Mixer):
             scratch = torch.empty((T, self.nq, self.nkv, self.vd), dtype=torch.float32, device=x.device)
         kernels.window_attention(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.tables["k"], self.scale,
                                  self.window, ctx.status, dist_bias=self.dist_table, sink=self.sink,
-                                 softcap=self.softcap, talk=self.talk, scratch=scratch, **pooled)
+                                 softcap=self.softcap, talk=self.talk, scratch=scratch,
+                                 n_requests=int(ctx.req_start.numel()) - 1, **pooled)
         y = linear(out.view(T, self.nq * self.vd), self.w_o, out_dtype=torch.float32)
         return Addends(y, bias=self.b_o) if self.biases else y

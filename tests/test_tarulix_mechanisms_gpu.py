@@ -78,7 +78,19 @@ def _attend(cache, q, rows, scale, window, dtype, **opts):
     if cache.pool:
         opts.update(pool=cache.pool, pooled_k=cache.kp, pooled_v=cache.vp, pool_table=cache.ptable)
     kernels.window_attention(q.to(dtype).to(DEV), cache.k, cache.v, out, pos, req, cache.table, scale, window,
-                             cache.status, **opts)
+                             cache.status, n_split=1, tensor_cores=False, **opts)
+    # the other ways the same launch can run: the keys of every token cut into ranges that are joined afterwards
+    # (steps of few tokens), and scores and sums on the tensor cores (long portions, the shapes that path takes);
+    # each must give what one warp a (token, head) gives
+    others = {"ranges_2": dict(n_split=2, tensor_cores=False), "ranges_7": dict(n_split=7, tensor_cores=False)}
+    if kernels.window_attention_uses_tensor_cores(dtype, q.shape[2], vd):
+        others["tensor_cores"] = dict(tensor_cores=True)
+    tol = 2e-5 if dtype == torch.float32 else 1.6e-2
+    for name, how in others.items():
+        alt = torch.full_like(out, float("nan"))
+        kernels.window_attention(q.to(dtype).to(DEV), cache.k, cache.v, alt, pos, req, cache.table, scale, window,
+                                 cache.status, **how, **opts)
+        assert torch.allclose(alt.float(), out.float(), atol=tol, rtol=tol), (name, float((alt.float() - out.float()).abs().max()))
     torch.cuda.synchronize()
     assert int(cache.status.cpu()[0]) == 0
     return out.float().cpu()
@@ -92,7 +104,7 @@ def _bias_rows_by_distance(rel, window, far):
 SHAPES = [
     # heads, kv heads, key size, value size, window, page
     (4, 2, 16, 24, 9, 4), (6, 1, 20, 12, 33, 8), (3, 3, 64, 64, 17, 16), (8, 2, 128, 64, 70, 16), (2, 1, 40, 8, 1, 4),
-    (4, 4, 64, 128, 200, 16),
+    (4, 4, 64, 128, 200, 16), (4, 2, 48, 80, 40, 8), (2, 1, 96, 96, 72, 16), (4, 1, 256, 112, 100, 16), (2, 2, 16, 16, 64, 4),
 ]
 
 
