@@ -385,7 +385,7 @@ def window_attn(tokens_per_req: int, reqs: int, context: int, nq: int, nkv: int,
 
 
 def scan(tokens_per_req: int, reqs: int, inner: int, N: int, rank: int) -> dict:
-    """``selective_scan`` alone (step sizes and the chain in time).  Bytes: the state read and written, and per token
+    """``selective_scan`` alone (the float32 step projection, a library product, and the chain in time).  Bytes: the state read and written, and per token
     u (bfloat16), z, dt written and read, the output (bfloat16) and the projection row."""
     import torch
     import bench_kernels as bk
@@ -395,7 +395,7 @@ def scan(tokens_per_req: int, reqs: int, inner: int, N: int, rank: int) -> dict:
     u = torch.randn(T, inner, device=dev, dtype=torch.bfloat16)
     proj = torch.randn(T, rank + 2 * N, device=dev)
     z = torch.randn(T, inner, device=dev)
-    w_dt = torch.randn(rank, inner, device=dev) / rank ** 0.5
+    w_dt = torch.randn(inner, rank, device=dev) / rank ** 0.5
     dt_b, D = torch.zeros(inner, device=dev), torch.ones(inner, device=dev)
     A = -torch.exp(torch.rand(inner, N, device=dev))
     layers = 1 if tokens_per_req > 1 else max(1, min(16, int(2e9 // (reqs * inner * N * 4))))
@@ -406,7 +406,7 @@ def scan(tokens_per_req: int, reqs: int, inner: int, N: int, rank: int) -> dict:
 
     def all_layers():
         for s in states:
-            k.selective_scan(u, proj, z, w_dt, dt_b, A, D, s, out, starts, slots, rank, N)
+            k.selective_scan(u, proj, z, torch.mm(proj[:, :rank], w_dt.t()), dt_b, A, D, s, out, starts, slots, rank, N)
     ms = (bk.timed_graph(all_layers, reps=1) if tokens_per_req == 1 else bk.timed(all_layers, n=5, warm=2)) / layers
     nbytes = 2 * reqs * inner * N * 4 + T * (inner * (2 + 4 + 8 + 2) + (rank + 2 * N) * 4) + inner * (rank + N + 2) * 4
     flops = T * inner * (2.0 * rank + 7.0 * N)

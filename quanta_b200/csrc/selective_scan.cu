@@ -11,10 +11,11 @@
 // of the convolution that also feeds the projection of low, B and C), `proj` holds that projection's float32
 // accumulators [low | B | C] and z comes from the float32 rows of the input projection.
 //
-// Two launches: the step sizes of all tokens at once, then the chain in time: eight lanes own a channel (each a
-// stride-8 share of its N states, in registers), a block owns 16 channels of one request and walks the request's
-// rows of this step in order.  Single tokens and portions are the same code and a channel's arithmetic does not
-// depend on which block owns it, so cut and batch change nothing.
+// The step projection W_dt low is a library product (float32) that the caller hands in; its bias and softplus are
+// applied as the chain reads it.  The chain in time: eight lanes own a channel (each a stride-8 share of its N
+// states, in registers), a block owns 16 channels of one request and walks the request's rows of this step in
+// order, a chunk of tokens at a time through shared memory.  Single tokens and portions are the same code and a
+// channel's arithmetic does not depend on which block owns it, so cut and batch change nothing.
 #include "common.cuh"
 
 constexpr int SS_LANES = 8;            // lanes that share a channel
@@ -23,27 +24,14 @@ constexpr int SS_MAX_STATE = 256;
 
 __device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-// dt[t, c] for all tokens: a thread a (token, channel); w_dt is stored [R, inner], so the threads of a warp
-// (neighbouring channels of one token) read neighbouring numbers
-__global__ void scan_steps_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ w_dt_t,
-                                  const float* __restrict__ dt_bias, float* __restrict__ dt, int T, int inner, int R) {
-  const size_t n = (size_t)T * inner;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const int t = (int)(i / inner), c = (int)(i % inner);
-    const float* low = proj + (size_t)t * proj_stride;
-    float acc = 0.f;
-    for (int r = 0; r < R; ++r) acc = fmaf(w_dt_t[(size_t)r * inner + c], low[r], acc);
-    dt[i] = ss_softplus(acc + dt_bias[c]);
-  }
-}
-
 // NPL: states a lane holds, N <= 8 * NPL.  The request's rows are walked in chunks of `tok` tokens: the block first
 // brings the chunk's step sizes, inputs and B / C vectors into shared memory (all threads, whole segments of the
 // rows), then every lane runs the chunk's steps from there (nothing in the chain waits for global memory), then
 // the block gates and writes the chunk's outputs.
 template <typename U, typename O, int NPL>
 __global__ void __launch_bounds__(SS_CH * SS_LANES)
-scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const float* __restrict__ proj,
+scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt_pre, const float* __restrict__ dt_bias,
+                  const float* __restrict__ proj,
                   int proj_stride, int b_off, int c_off, const float* __restrict__ z, int z_stride,
                   const float* __restrict__ A, const float* __restrict__ D, float* __restrict__ state,
                   O* __restrict__ out, const int* __restrict__ req_start, const int* __restrict__ req_slot, int inner,
@@ -75,7 +63,7 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const f
     const int nt = min(tok, last - t0);
     for (int i = threadIdx.x; i < nt * SS_CH; i += blockDim.x) {
       const int tt = i / SS_CH, k = min(c0 + i % SS_CH, inner - 1);
-      s_dt[i] = dt[(size_t)(t0 + tt) * inner + k];
+      s_dt[i] = ss_softplus(dt_pre[(size_t)(t0 + tt) * inner + k] + dt_bias[k]);
       s_u[i] = qb_to_float<U>(u[(size_t)(t0 + tt) * inner + k]);
     }
     for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
@@ -85,24 +73,44 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const f
       s_C[i] = row[c_off + n];
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float dtv = s_dt[tt * SS_CH + ch];
-      const float uv = s_u[tt * SS_CH + ch];
-      const float* Bt = s_B + tt * N;
-      const float* Ct = s_C + tt * N;
-      const float du = dtv * uv;
-      float y = 0.f;
+    // U steps at a time: their decays, inputs and output vectors are formed first (nothing of that waits for the
+    // state), then the state walks through them, then the U sums are added up across the lanes side by side
+    constexpr int U = NPL <= 4 ? 4 : NPL <= 8 ? 2 : 1;
+    for (int tt = 0; tt < nt; tt += U) {
+      float dec[U][NPL], inb[U][NPL], cv[U][NPL], uvs[U], y[U];
 #pragma unroll
-      for (int i = 0; i < NPL; ++i) {
-        const int n = sub + SS_LANES * i;
-        if (n < N) {
-          S[i] = fmaf(expf(dtv * a[i]), S[i], du * Bt[n]);
-          y = fmaf(S[i], Ct[n], y);
+      for (int s = 0; s < U; ++s) {
+        const int row = min(tt + s, nt - 1);
+        const float dtv = s_dt[row * SS_CH + ch];
+        uvs[s] = s_u[row * SS_CH + ch];
+        const float du = dtv * uvs[s];
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+          const int n = sub + SS_LANES * i;
+          dec[s][i] = n < N ? expf(dtv * a[i]) : 0.f;
+          inb[s][i] = n < N ? du * s_B[row * N + n] : 0.f;
+          cv[s][i] = n < N ? s_C[row * N + n] : 0.f;
         }
       }
 #pragma unroll
-      for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (sub == 0) s_y[tt * SS_CH + ch] = fmaf(d_c, uv, y);
+      for (int s = 0; s < U; ++s) {
+        y[s] = 0.f;
+        if (tt + s < nt) {
+#pragma unroll
+          for (int i = 0; i < NPL; ++i) {
+            S[i] = fmaf(dec[s][i], S[i], inb[s][i]);
+            y[s] = fmaf(S[i], cv[s][i], y[s]);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = SS_LANES / 2; o > 0; o >>= 1) {
+#pragma unroll
+        for (int s = 0; s < U; ++s) y[s] += __shfl_xor_sync(0xffffffffu, y[s], o);
+      }
+#pragma unroll
+      for (int s = 0; s < U; ++s)
+        if (sub == 0 && tt + s < nt) s_y[(tt + s) * SS_CH + ch] = fmaf(d_c, uvs[s], y[s]);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nt * SS_CH; i += blockDim.x) {
@@ -125,19 +133,16 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt, const f
 }
 
 // u [T, inner] in the activation dtype; proj float32 rows [low (R) | B (N) | C (N) | ...]; z float32 rows of
-// z_stride; w_dt_t float32 [R, inner] (the step projection, transposed); A float32 [inner, N] (already -exp(A_log)); state float32 [slots, inner, N];
-// dt float32 scratch [T, inner]; out [T, inner] in the activation dtype.
+// z_stride; dt_pre float32 [T, inner], the step projection of `low` (a library product) before its bias and
+// softplus; A float32 [inner, N] (already -exp(A_log)); state float32 [slots, inner, N]; out [T, inner] in the
+// activation dtype.
 extern "C" int qb_selective_scan(const void* u, int dtype, const float* proj, int proj_stride, const float* z,
-                                 int z_stride, const float* w_dt, const float* dt_bias, const float* A, const float* D,
-                                 float* state, float* dt, void* out, const int* req_start, const int* req_slot, int T,
+                                 int z_stride, const float* dt_pre, const float* dt_bias, const float* A, const float* D,
+                                 float* state, void* out, const int* req_start, const int* req_slot, int T,
                                  int R_req, int inner, int N, int rank, cudaStream_t stream) {
   if (T <= 0 || R_req <= 0) return 0;
   if (inner <= 0 || N <= 0 || rank <= 0 || proj_stride < rank + 2 * N || z_stride < inner) return QB_ERR_BAD_ARG;
   if (N > SS_MAX_STATE || R_req > 65535) return QB_ERR_UNSUPPORTED;
-  const size_t n = (size_t)T * inner;
-  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
-  scan_steps_kernel<<<blocks, 256, 0, stream>>>(proj, proj_stride, w_dt, dt_bias, dt, T, inner, rank);
-  QB_LAUNCH_CHECK();
   dim3 grid((inner + SS_CH - 1) / SS_CH, R_req);
   // tokens a chunk: at most 32, at most the longest portion can be, and what 44 KB of shared memory hold
   const int per_tok = (3 * SS_CH + 2 * N) * (int)sizeof(float);
@@ -147,7 +152,8 @@ extern "C" int qb_selective_scan(const void* u, int dtype, const float* proj, in
   const size_t smem = (size_t)tok * per_tok;
 #define QB_SS_LAUNCH(NPL)                                                                                             \
   QB_DISPATCH_DTYPE(dtype, U, (scan_chain_kernel<U, U, NPL><<<grid, SS_CH * SS_LANES, smem, stream>>>(                \
-      (const U*)u, dt, proj, proj_stride, rank, rank + N, z, z_stride, A, D, state, (U*)out, req_start, req_slot, inner, N, \
+      (const U*)u, dt_pre, dt_bias, proj, proj_stride, rank, rank + N, z, z_stride, A, D, state, (U*)out, req_start,  \
+      req_slot, inner, N,                                                                                             \
       tok)))
   if (N <= 8 * 2) QB_SS_LAUNCH(2);
   else if (N <= 8 * 4) QB_SS_LAUNCH(4);

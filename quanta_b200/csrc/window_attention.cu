@@ -59,8 +59,8 @@ struct WaParams {
   const float* sink;           // [nq] or null
   int all_values;              // 1: every head's weights on the values of all kv heads (scratch), 0: its own
   int vec;
-  int n_split;                 // > 1: a warp takes one of n_split ranges of the keys and leaves (max, sum, sums of
-  float* part;                 // values) in `part` [T, nq, n_split, 2 + (all_values ? nkv : 1) * vd] for the merge
+  int n_split;                 // > 1 (the ranges kernel): a warp takes one of n_split ranges of the keys and leaves (max,
+  float* part;                 // sum, sums of values) in `part` [T, nq, n_split, 2 + (all_values ? nkv : 1) * vd]
   int* status;
 };
 
@@ -73,9 +73,8 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
   extern __shared__ float wa_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long wid = (long)blockIdx.x * WA_WARPS + warp;
-  if (wid >= (long)P.T * P.nq * P.n_split) return;
-  const int split = (int)(wid % P.n_split);
-  const int t = (int)(wid / P.n_split / P.nq), h = (int)(wid / P.n_split % P.nq);
+  if (wid >= (long)P.T * P.nq) return;
+  const int t = (int)(wid / P.nq), h = (int)(wid % P.nq);
   const int nq = P.nq, nkv = P.nkv, hd = P.hd, vd = P.vd, ps = P.page_size;
   const int kvh = h / (nq / nkv);
   const int GV = P.all_values ? nkv : 1;
@@ -95,22 +94,18 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
   // pooled blocks that lie wholly before the window: b * pool + pool - 1 <= pos - window
   const int n_blocks = (pt != nullptr && P.window > 0 && pos - P.window + 1 >= P.pool) ? (pos - P.window + 1) / P.pool : 0;
   const int n_keys = n_blocks + (pos - lo + 1);
-  // this warp's range of the keys: whole rounds of 32
-  const int per_split = ((n_keys + P.n_split - 1) / P.n_split + 31) / 32 * 32;
-  const int k_begin = split * per_split;
-  const int k_end = min(n_keys, k_begin + per_split);
 
   float m = -INFINITY, l = 0.f;
   float acc[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) acc[i] = 0.f;
 
-  for (int k0 = k_begin; k0 < k_end; k0 += 32) {
+  for (int k0 = 0; k0 < n_keys; k0 += 32) {
     const int idx = k0 + lane;
     float s = -INFINITY;
     long base = -1;       // row of this lane's key among all (page, kv head 0, slot) rows; + m * page_size for kv head m
     int pooled = 0;
-    if (idx < k_end) {
+    if (idx < n_keys) {
       pooled = idx < n_blocks;
       const int row = pooled ? idx : lo + (idx - n_blocks);       // pooled row or token position
       const int page = pooled ? pt[row / ps] : bt[row / ps];
@@ -142,7 +137,7 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
     const float corr = expf(m - m_new);
     l = l * corr + qb_warp_sum(p);
     m = m_new;
-    const int n_here = min(32, k_end - k0);
+    const int n_here = min(32, n_keys - k0);
     for (int g = 0; g < GV; ++g) {
       const int vh = P.all_values ? g : kvh;
       if (P.all_values) {
@@ -175,20 +170,6 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
       }
     }
   }
-  if (P.n_split > 1) {
-    float* prow = P.part + (size_t)wid * (2 + GV * vd);
-    if (lane == 0) { prow[0] = m; prow[1] = l; }
-    if (P.all_values) {
-      for (int i = lane; i < nkv * vd; i += 32) prow[2 + i] = acc_sm[i];
-    } else {
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int d = lane + 32 * i;
-        if (d < vd) prow[2 + d] = acc[i];
-      }
-    }
-    return;
-  }
   float denom = l;
   if (P.sink != nullptr) denom += (m == -INFINITY) ? 1.f : expf(P.sink[h] - m);
   const float inv_l = denom > 0.f ? 1.f / denom : 0.f;
@@ -205,57 +186,226 @@ window_attention_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, 
   }
 }
 
-// The ranges of a (token, head) joined: with M = max of the ranges' maxima, weight_r = exp(m_r - M) / (sum_r l_r
-// exp(m_r - M) + exp(sink - M)); the normed sums of values go to `out` (own kv head) or, when the heads' weights
-// are mixed afterwards, to scratch [T, nq, nkv, vd].  One block per token; its shared memory holds the weights
-// [nq, n_split].
-template <typename A>
-__global__ void wa_merge_kernel(const float* __restrict__ part, const float* __restrict__ sink, A* __restrict__ out,
-                                float* __restrict__ scratch, int T, int nq, int nkv, int vd, int n_split, int all_values) {
-  extern __shared__ float wm_w[];
-  const int t = blockIdx.x;
-  if (t >= T) return;
-  const int GV = all_values ? nkv : 1;
-  const size_t stride = 2 + (size_t)GV * vd;
-  const float* prow = part + (size_t)t * nq * n_split * stride;
-  for (int h = threadIdx.x; h < nq; h += blockDim.x) {
-    float M = -INFINITY;
-    for (int r = 0; r < n_split; ++r) M = fmaxf(M, prow[((size_t)h * n_split + r) * stride]);
-    float denom = 0.f;
-    for (int r = 0; r < n_split; ++r) {
-      const float* pr = prow + ((size_t)h * n_split + r) * stride;
-      const float e = pr[0] == -INFINITY ? 0.f : expf(pr[0] - M);
-      wm_w[h * n_split + r] = e;
-      denom += pr[1] * e;
-    }
-    if (sink != nullptr) denom += (M == -INFINITY) ? 1.f : expf(sink[h] - M);
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    for (int r = 0; r < n_split; ++r) wm_w[h * n_split + r] *= inv;
+// NV consecutive elements from an address that is a multiple of NV elements
+template <typename A, int NV>
+__device__ __forceinline__ void wa_load_run(const A* p, float* o) {
+  struct alignas(sizeof(A) * NV) Run { A v[NV]; };
+  const Run r = *reinterpret_cast<const Run*>(p);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) o[i] = qb_to_float<A>(r.v[i]);
+}
+
+// Steps of few tokens: a warp takes one of n_split ranges of a token's keys for up to GQ q heads that share a kv
+// head: a key row is read once for all of them (lanes own keys), a value row once (lanes own NV neighbouring
+// dims).  It leaves (max, sum, sums of values) per head in `part` [T, nq, n_split, 2 + GV * vd] for the join;
+// with all_values one warp per kv head whose values the heads' weights are applied to (GV = nkv).
+template <typename A, int NV, int GQ>
+__global__ void __launch_bounds__(WA_WARPS * 32)
+window_attention_ranges_kernel(const A* __restrict__ q, const A* __restrict__ k_cache, const A* __restrict__ v_cache,
+                               const A* __restrict__ kp_cache, const A* __restrict__ vp_cache, const WaParams P) {
+  extern __shared__ float wa_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nq = P.nq, nkv = P.nkv, hd = P.hd, vd = P.vd, ps = P.page_size;
+  const int group = nq / nkv, n_chunks = (group + GQ - 1) / GQ, GV = P.all_values ? nkv : 1;
+  long wid = (long)blockIdx.x * WA_WARPS + warp;
+  if (wid >= (long)P.T * nkv * n_chunks * P.n_split * GV) return;
+  const int vsel = (int)(wid % GV); wid /= GV;
+  const int split = (int)(wid % P.n_split); wid /= P.n_split;
+  const int chunk = (int)(wid % n_chunks); wid /= n_chunks;
+  const int kvh = (int)(wid % nkv);
+  const int t = (int)(wid / nkv);
+  const int h0 = kvh * group + chunk * GQ;
+  const int n_g = min(GQ, group - chunk * GQ);
+  const int vh = P.all_values ? vsel : kvh;
+  float* qs = wa_smem + (size_t)warp * GQ * hd;
+  for (int i = lane; i < GQ * hd; i += 32) {
+    const int g = i / hd, d = i % hd;
+    qs[i] = g < n_g ? qb_to_float<A>(q[((size_t)t * nq + h0 + g) * hd + d]) : 0.f;
   }
-  __syncthreads();
-  const int n = nq * GV * vd;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int h = i / (GV * vd), rest = i % (GV * vd);
-    float v = 0.f;
-    for (int r = 0; r < n_split; ++r)
-      v = fmaf(wm_w[h * n_split + r], prow[((size_t)h * n_split + r) * stride + 2 + rest], v);
-    if (all_values) scratch[(size_t)t * n + i] = v;
-    else out[(size_t)t * n + i] = qb_from_float<A>(v);
+  __syncwarp();
+
+  const int pos = P.tok_pos[t];
+  const int req = P.tok_req[t];
+  const int* bt = P.block_table + (size_t)req * P.bt_stride;
+  const int* pt = P.pool_table ? P.pool_table + (size_t)req * P.pool_stride : nullptr;
+  const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+  const int n_blocks = (pt != nullptr && P.window > 0 && pos - P.window + 1 >= P.pool) ? (pos - P.window + 1) / P.pool : 0;
+  const int n_keys = n_blocks + (pos - lo + 1);
+  const int per_split = ((n_keys + P.n_split - 1) / P.n_split + 31) / 32 * 32;
+  const int k_begin = split * per_split;
+  const int k_end = min(n_keys, k_begin + per_split);
+  const bool v_runs = vd == 32 * NV;
+
+  float m[GQ], l[GQ], acc[GQ][NV];
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[g][i] = 0.f;
+  }
+  for (int k0 = k_begin; k0 < k_end; k0 += 32) {
+    const int idx = k0 + lane;
+    float s[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) s[g] = -INFINITY;
+    long base = -1;
+    int pooled = 0;
+    if (idx < k_end) {
+      pooled = idx < n_blocks;
+      const int row = pooled ? idx : lo + (idx - n_blocks);
+      const int page = pooled ? pt[row / ps] : bt[row / ps];
+      if (page < 0 || page >= (pooled ? P.num_pool_pages : P.num_pages)) {
+        qb_set_status(P.status, QB_STATUS_BAD_PAGE, page, 3);
+      } else {
+        base = ((long)page * nkv) * ps + row % ps;
+        const A* kp = (pooled ? kp_cache : k_cache) + (base + (long)kvh * ps) * hd;
+        float dot[GQ];
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) dot[g] = 0.f;
+        if (P.vec) {
+          for (int d = 0; d < hd; d += WaVec<A>::N) {
+            float kv[WaVec<A>::N];
+            WaVec<A>::load(kp + d, kv);
+#pragma unroll
+            for (int g = 0; g < GQ; ++g)
+#pragma unroll
+              for (int i = 0; i < WaVec<A>::N; ++i) dot[g] += qs[g * hd + d + i] * kv[i];
+          }
+        } else {
+          for (int d = 0; d < hd; ++d) {
+            const float kv = qb_to_float<A>(kp[d]);
+#pragma unroll
+            for (int g = 0; g < GQ; ++g) dot[g] += qs[g * hd + d] * kv;
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          float x = dot[g] * P.scale;
+          if (P.cap > 0.f) x = P.cap * tanhf(x / P.cap);
+          if (P.dist_bias != nullptr && !pooled && g < n_g) x += P.dist_bias[(size_t)(pos - row) * nq + h0 + g];
+          s[g] = x;
+        }
+      }
+    }
+    if (!__any_sync(0xffffffffu, base >= 0)) continue;
+    float p[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const float m_new = fmaxf(m[g], qb_warp_max(s[g]));
+      p[g] = (base >= 0) ? expf(s[g] - m_new) : 0.f;
+      const float corr = expf(m[g] - m_new);
+      l[g] = l[g] * corr + qb_warp_sum(p[g]);
+      m[g] = m_new;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[g][i] *= corr;
+    }
+    const int n_here = min(32, k_end - k0);
+    // eight value rows are asked for before the first is used: with few warps on the device nothing else hides
+    // the time a row takes to arrive
+    for (int j0 = 0; j0 < n_here; j0 += 8) {
+      float v[8][NV];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const long bj = __shfl_sync(0xffffffffu, base, j0 + u);
+        const int pl = __shfl_sync(0xffffffffu, pooled, j0 + u);
+        const bool there = j0 + u < n_here && bj >= 0;
+        const A* vp = (pl ? vp_cache : v_cache) + (there ? (bj + (long)vh * ps) * vd : 0) + lane * NV;
+        if (v_runs) {
+          wa_load_run<A, NV>(vp, v[u]);
+#pragma unroll
+          for (int i = 0; i < NV; ++i) v[u][i] = there ? v[u][i] : 0.f;
+        } else {
+#pragma unroll
+          for (int i = 0; i < NV; ++i) v[u][i] = (there && lane * NV + i < vd) ? qb_to_float<A>(vp[i]) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          const float pj = __shfl_sync(0xffffffffu, p[g], j0 + u);
+#pragma unroll
+          for (int i = 0; i < NV; ++i) acc[g][i] = fmaf(pj, v[u][i], acc[g][i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    if (g >= n_g) continue;
+    float* prow = P.part + (((size_t)t * nq + h0 + g) * P.n_split + split) * (2 + (size_t)GV * vd);
+    if (lane == 0 && vsel == 0) { prow[0] = m[g]; prow[1] = l[g]; }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = lane * NV + i;
+      if (d < vd) prow[2 + (size_t)vsel * vd + d] = acc[g][i];
+    }
   }
 }
 
-// out[t, h, :] = sum_g talk[h, g] * scratch[t, g, kv(h), :], g ascending.  One block per token.
+// The ranges of a (token, head) joined: with M = max of the ranges' maxima, weight_r = exp(m_r - M) / (sum_r l_r
+// exp(m_r - M) + exp(sink - M)); the normed sums of values go to `out` (own kv head) or, when the heads' weights
+// are mixed afterwards, to scratch [T, nq, nkv, vd].  One block per (token, head); its shared memory holds the
+// ranges' weights; eight ranges are read before the first is used.
 template <typename A>
-__global__ void talk_mix_kernel(const float* __restrict__ scratch, const float* __restrict__ talk, A* __restrict__ out,
-                                int T, int nq, int nkv, int vd) {
-  const int t = blockIdx.x;
+__global__ void __launch_bounds__(128)
+wa_merge_kernel(const float* __restrict__ part, const float* __restrict__ sink, A* __restrict__ out,
+                float* __restrict__ scratch, int T, int nq, int nkv, int vd, int n_split, int all_values) {
+  extern __shared__ float wm_w[];                       // [n_split]
+  const int t = blockIdx.x / nq, h = blockIdx.x % nq;
   if (t >= T) return;
-  const float* srow = scratch + (size_t)t * nq * nkv * vd;
-  for (int i = threadIdx.x; i < nq * vd; i += blockDim.x) {
-    const int h = i / vd, d = i % vd;
-    const int kvh = h / (nq / nkv);
+  const int GV = all_values ? nkv : 1;
+  const size_t stride = 2 + (size_t)GV * vd;
+  const float* prow = part + ((size_t)t * nq + h) * n_split * stride;
+  for (int r = threadIdx.x; r < n_split; r += blockDim.x) wm_w[r] = prow[r * stride];
+  __syncthreads();
+  float M = -INFINITY;
+  for (int r = 0; r < n_split; ++r) M = fmaxf(M, wm_w[r]);
+  __syncthreads();
+  for (int r = threadIdx.x; r < n_split; r += blockDim.x) {
+    const float mr = prow[r * stride];
+    wm_w[r] = mr == -INFINITY ? 0.f : expf(mr - M);
+  }
+  __syncthreads();
+  float denom = 0.f;
+  for (int r = 0; r < n_split; ++r) denom = fmaf(prow[r * stride + 1], wm_w[r], denom);
+  if (sink != nullptr) denom += (M == -INFINITY) ? 1.f : expf(sink[h] - M);
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  const int n = GV * vd;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float v = 0.f;
-    for (int g = 0; g < nq; ++g) v = fmaf(talk[h * nq + g], srow[((size_t)g * nkv + kvh) * vd + d], v);
+    for (int r0 = 0; r0 < n_split; r0 += 8) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) x[u] = r0 + u < n_split ? prow[(size_t)(r0 + u) * stride + 2 + i] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v = r0 + u < n_split ? fmaf(wm_w[r0 + u], x[u], v) : v;
+    }
+    v *= inv;
+    if (all_values) scratch[((size_t)t * nq + h) * n + i] = v;
+    else out[((size_t)t * nq + h) * n + i] = qb_from_float<A>(v);
+  }
+}
+
+// out[t, h, :] = sum_g talk[h, g] * scratch[t, g, kv(h), :], g ascending.  One block per (token, head).
+template <typename A>
+__global__ void __launch_bounds__(128)
+talk_mix_kernel(const float* __restrict__ scratch, const float* __restrict__ talk, A* __restrict__ out, int T, int nq,
+                int nkv, int vd) {
+  const int t = blockIdx.x / nq, h = blockIdx.x % nq;
+  if (t >= T) return;
+  const int kvh = h / (nq / nkv);
+  const float* srow = scratch + (size_t)t * nq * nkv * vd + (size_t)kvh * vd;
+  const float* trow = talk + (size_t)h * nq;
+  for (int d = threadIdx.x; d < vd; d += blockDim.x) {
+    float v = 0.f;
+    for (int g0 = 0; g0 < nq; g0 += 8) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) x[u] = g0 + u < nq ? srow[(size_t)(g0 + u) * nkv * vd + d] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v = g0 + u < nq ? fmaf(trow[g0 + u], x[u], v) : v;
+    }
     out[((size_t)t * nq + h) * vd + d] = qb_from_float<A>(v);
   }
 }
@@ -281,11 +431,48 @@ extern "C" int qb_window_attention(const void* q, int dtype, const void* k_cache
   P.dist_bias = dist_bias; P.sink = sink; P.all_values = talk != nullptr; P.status = status;
   P.vec = (hd % 8 == 0 && ((uintptr_t)k_cache & 15) == 0 && (kp_cache == nullptr || ((uintptr_t)kp_cache & 15) == 0)) ? 1 : 0;
   P.n_split = n_split; P.part = part;
-  const long warps = (long)T * nq * n_split;
+  const int nv = (vd + 31) / 32;
+  if (n_split > 1) {
+    const int group = nq / nkv;
+    const int gq = group > 4 ? 8 : group > 2 ? 4 : group > 1 ? 2 : 1;
+    const int n_chunks = (group + gq - 1) / gq;
+    const long rw = (long)T * nkv * n_chunks * n_split * (P.all_values ? nkv : 1);
+    const int rblocks = (int)((rw + WA_WARPS - 1) / WA_WARPS);
+    const size_t rsmem = (size_t)WA_WARPS * gq * hd * sizeof(float);
+#define QB_WR_LAUNCH(A, NV, GQ)                                                                                   \
+    window_attention_ranges_kernel<A, NV, GQ><<<rblocks, WA_WARPS * 32, rsmem, stream>>>(                           \
+        (const A*)q, (const A*)k_cache, (const A*)v_cache, (const A*)kp_cache, (const A*)vp_cache, P)
+#define QB_WR_GROUP(A, NV)                                                                                        \
+    do {                                                                                                          \
+      if (gq == 1) QB_WR_LAUNCH(A, NV, 1);                                                                        \
+      else if (gq == 2) QB_WR_LAUNCH(A, NV, 2);                                                                   \
+      else if (gq == 4) QB_WR_LAUNCH(A, NV, 4);                                                                   \
+      else QB_WR_LAUNCH(A, NV, 8);                                                                                \
+    } while (0)
+    QB_DISPATCH_DTYPE(dtype, A, {
+      if (nv <= 1) QB_WR_GROUP(A, 1);
+      else if (nv <= 2) QB_WR_GROUP(A, 2);
+      else if (nv <= 4) QB_WR_GROUP(A, 4);
+      else QB_WR_GROUP(A, 8);
+    });
+#undef QB_WR_GROUP
+#undef QB_WR_LAUNCH
+    QB_LAUNCH_CHECK();
+    const size_t wsm = (size_t)n_split * sizeof(float);
+    if (wsm > 48 * 1024 || (long)T * nq > 0x7fffffffL) return QB_ERR_UNSUPPORTED;
+    QB_DISPATCH_DTYPE(dtype, A, wa_merge_kernel<A><<<T * nq, 128, wsm, stream>>>(part, sink, (A*)out, scratch, T, nq, nkv,
+                                                                                vd, n_split, P.all_values));
+    QB_LAUNCH_CHECK();
+    if (talk != nullptr) {
+      QB_DISPATCH_DTYPE(dtype, A, talk_mix_kernel<A><<<T * nq, 128, 0, stream>>>(scratch, talk, (A*)out, T, nq, nkv, vd));
+      QB_LAUNCH_CHECK();
+    }
+    return 0;
+  }
+  const long warps = (long)T * nq;
   const int blocks = (int)((warps + WA_WARPS - 1) / WA_WARPS);
   const size_t smem = (size_t)WA_WARPS * (hd + (P.all_values ? nkv * vd : 0)) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
-  const int nv = (vd + 31) / 32;
 #define QB_WA_LAUNCH(A, NV)                                                                                      \
   do {                                                                                                           \
     auto kern = window_attention_kernel<A, NV>;                                                                  \
@@ -304,15 +491,8 @@ extern "C" int qb_window_attention(const void* q, int dtype, const void* k_cache
   });
 #undef QB_WA_LAUNCH
   QB_LAUNCH_CHECK();
-  if (n_split > 1) {
-    const size_t wsm = (size_t)nq * n_split * sizeof(float);
-    if (wsm > 48 * 1024) return QB_ERR_UNSUPPORTED;
-    QB_DISPATCH_DTYPE(dtype, A, wa_merge_kernel<A><<<T, 256, wsm, stream>>>(part, sink, (A*)out, scratch, T, nq, nkv, vd,
-                                                                           n_split, P.all_values));
-    QB_LAUNCH_CHECK();
-  }
   if (talk != nullptr) {
-    QB_DISPATCH_DTYPE(dtype, A, talk_mix_kernel<A><<<T, 256, 0, stream>>>(scratch, talk, (A*)out, T, nq, nkv, vd));
+    QB_DISPATCH_DTYPE(dtype, A, talk_mix_kernel<A><<<T * nq, 128, 0, stream>>>(scratch, talk, (A*)out, T, nq, nkv, vd));
     QB_LAUNCH_CHECK();
   }
   return 0;
@@ -422,9 +602,11 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   const int hd = P.hd, vd = P.vd, nq = P.nq, nkv = P.nkv, ps = P.page_size;
   const int pq = hd + 8, pv = vd + 8;                                  // row pitches in elements (16-byte multiples)
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);      // [64][pq]
-  __nv_bfloat16* Ks = Qs + WM_BM * pq;                                 // [64][pq]
-  __nv_bfloat16* Vs = Ks + WM_BN * pq;                                 // [64][pv]
-  int* s_pos = reinterpret_cast<int*>(Vs + WM_BN * pv);                // [64]
+  __nv_bfloat16* Ks0 = Qs + WM_BM * pq;                                // [2][64][pq]
+  __nv_bfloat16* Vs0 = Ks0 + 2 * WM_BN * pq;                           // [2][64][pv]
+  long long* s_base = reinterpret_cast<long long*>(Vs0 + 2 * WM_BN * pv);   // [2][64] cache row of a key, * 2 + pooled
+  float* s_bias0 = reinterpret_cast<float*>(s_base + 2 * WM_BN);       // [2][128] the biases by distance of a tile
+  int* s_pos = reinterpret_cast<int*>(s_bias0 + 4 * WM_BN);            // [64]
   int* s_req = s_pos + WM_BM;                                          // [64]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
@@ -480,32 +662,79 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const bool mine_a = req_a == req && r_a >= ra && r_a < rb, mine_b = req_b == req && r_b >= ra && r_b < rb;
     const int* bt = P.block_table + (size_t)req * P.bt_stride;
     const int* pt = pooling ? P.pool_table + (size_t)req * P.pool_stride : nullptr;
+    // what the warp's 16 rows have in common: a tile of token keys that every one of them sees in full needs no
+    // mask, and with neighbouring positions its biases sit at fixed places of the tile's bias row
+    const bool w_whole = __all_sync(0xffffffffu, mine_a && mine_b);
+    const int w_lo_max = __reduce_max_sync(0xffffffffu, max(lo_a, lo_b));
+    const int w_pos_min = __reduce_min_sync(0xffffffffu, min(pos_a, pos_b));
 
-    for (int k0 = 0; k0 < n_keys; k0 += WM_BN) {
-      __syncthreads();                                                 // the last tile has been read by all warps
+    // the rows of the request's tokens in this tile and the distances that a tile of keys can be away from them
+    int pos_min = 0x7fffffff;
+    for (int r = ra; r < rb; ++r) pos_min = min(pos_min, s_pos[r]);
+
+    // a tile's keys: which cache row each is (one lookup a key), then 16-byte asynchronous copies of the rows'
+    // pieces into one of two buffers; the next tile's copies run while this tile is computed
+    auto find_rows = [&](int k0, int buf) {
+      if (tid < WM_BN) {
+        const int idx = k0 + tid;
+        long long enc = -1;
+        if (idx < n_keys) {
+          const bool pooled = idx < nb_max;
+          const int row = pooled ? idx : lo_min + (idx - nb_max);
+          const int page = pooled ? pt[row / ps] : bt[row / ps];
+          if (page < 0 || page >= (pooled ? P.num_pool_pages : P.num_pages)) qb_set_status(P.status, QB_STATUS_BAD_PAGE, page, 3);
+          else enc = ((((long long)page * nkv) * ps + row % ps) << 1) | (pooled ? 1 : 0);
+        }
+        s_base[buf * WM_BN + tid] = enc;
+      }
+    };
+    auto start_copies = [&](int buf) {
+      __nv_bfloat16* Kd = Ks0 + buf * WM_BN * pq;
+      __nv_bfloat16* Vd = Vs0 + buf * WM_BN * pv;
       for (int i = tid; i < WM_BN * (qc + vc); i += 128) {
         const bool is_k = i < WM_BN * qc;
         const int j = is_k ? i : i - WM_BN * qc;
         const int w = is_k ? qc : vc;
         const int r = j / w, c = j % w;
-        const int idx = k0 + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (idx < n_keys) {
-          const bool pooled = idx < nb_max;
-          const int row = pooled ? idx : lo_min + (idx - nb_max);
-          const int page = pooled ? pt[row / ps] : bt[row / ps];
-          if (page < 0 || page >= (pooled ? P.num_pool_pages : P.num_pages)) {
-            qb_set_status(P.status, QB_STATUS_BAD_PAGE, page, 3);
-          } else {
-            const size_t base = ((size_t)page * nkv) * ps + row % ps;
-            if (is_k) v = *reinterpret_cast<const uint4*>((pooled ? kp_cache : k_cache) + (base + (size_t)kvh_k * ps) * hd + c * 8);
-            else v = *reinterpret_cast<const uint4*>((pooled ? vp_cache : v_cache) + (base + (size_t)kvh_v * ps) * vd + c * 8);
-          }
-        }
-        if (is_k) *reinterpret_cast<uint4*>(Ks + r * pq + c * 8) = v;
-        else *reinterpret_cast<uint4*>(Vs + r * pv + c * 8) = v;
+        const long long enc = s_base[buf * WM_BN + r];
+        const bool pooled = enc >= 0 && (enc & 1);
+        const size_t base = enc >= 0 ? (size_t)(enc >> 1) : 0;
+        const __nv_bfloat16* src = is_k ? (pooled ? kp_cache : k_cache) + (base + (size_t)kvh_k * ps) * hd + c * 8
+                                        : (pooled ? vp_cache : v_cache) + (base + (size_t)kvh_v * ps) * vd + c * 8;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(is_k ? Kd + r * pq + c * 8 : Vd + r * pv + c * 8);
+        const int n = enc >= 0 ? 16 : 0;                               // 0: the 16 bytes are filled with zeros
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" :: "r"(dst), "l"(src), "r"(n));
       }
-      __syncthreads();
+      asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    __syncthreads();                                                   // the last request's tiles have been read
+    find_rows(0, 0);
+    __syncthreads();
+    start_copies(0);
+    int buf = 0;
+    for (int k0 = 0; k0 < n_keys; k0 += WM_BN, buf ^= 1) {
+      const bool more = k0 + WM_BN < n_keys;
+      if (more) find_rows(k0 + WM_BN, buf ^ 1);
+      // this tile's biases: distances d0 .. d0 + 127 cover every (row, key) pair when the request's positions in
+      // the tile are neighbours; pairs outside read the table itself
+      const int j_last = lo_min + (k0 + WM_BN - 1 - nb_max);
+      const int d0 = pos_min - j_last;
+      float* s_bias = s_bias0 + buf * 2 * WM_BN;                       // the other one may still be read
+      if (P.dist_bias != nullptr) {
+        const int d = d0 + tid;
+        s_bias[tid] = (d >= 0 && d < P.window) ? P.dist_bias[(size_t)d * nq + h] : 0.f;
+      }
+      __syncthreads();                                                 // the rows of the next tile are known, and
+      if (more) {                                                      // its buffer has been read by all warps
+        start_copies(buf ^ 1);
+        asm volatile("cp.async.wait_group 1;\n" ::);
+      } else {
+        asm volatile("cp.async.wait_group 0;\n" ::);
+      }
+      __syncthreads();                                                 // this tile's copies of all threads are there
+      const __nv_bfloat16* Ks = Ks0 + buf * WM_BN * pq;
+      const __nv_bfloat16* Vs = Vs0 + buf * WM_BN * pv;
       if (!warp_active) continue;
 
       float s[8][4];
@@ -523,6 +752,24 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       }
       // scale, cap, bias, mask
       float mx_a = -INFINITY, mx_b = -INFINITY;
+      const int j_first = lo_min + (k0 - nb_max);
+      const bool open_tile = w_whole && k0 >= nb_max && k0 + WM_BN <= n_keys && j_first >= w_lo_max &&
+                             j_first + WM_BN - 1 <= w_pos_min && pos_max - pos_min < WM_BM;
+      if (open_tile) {
+        const float* bias_a = s_bias + (pos_a - pos_min + WM_BN - 1 - 2 * t4);
+        const float* bias_b = s_bias + (pos_b - pos_min + WM_BN - 1 - 2 * t4);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float x = s[nt][e] * P.scale;
+            if (P.cap > 0.f) x = P.cap * tanhf(x / P.cap);
+            if (P.dist_bias != nullptr) x += (e >= 2 ? bias_b : bias_a)[-(nt * 8 + (e & 1))];
+            s[nt][e] = x;
+            if (e >= 2) mx_b = fmaxf(mx_b, x); else mx_a = fmaxf(mx_a, x);
+          }
+        }
+      } else {
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
@@ -543,13 +790,17 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
               if (j >= (second ? lo_b : lo_a) && j <= pos) {
                 x = s[nt][e] * P.scale;
                 if (P.cap > 0.f) x = P.cap * tanhf(x / P.cap);
-                if (P.dist_bias != nullptr) x += __ldg(P.dist_bias + (size_t)(pos - j) * nq + h);
+                if (P.dist_bias != nullptr) {
+                  const int dd = pos - j - d0;
+                  x += (dd >= 0 && dd < 2 * WM_BN) ? s_bias[dd] : __ldg(P.dist_bias + (size_t)(pos - j) * nq + h);
+                }
               }
             }
           }
           s[nt][e] = x;
           if (second) mx_b = fmaxf(mx_b, x); else mx_a = fmaxf(mx_a, x);
         }
+      }
       }
       mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
@@ -645,7 +896,8 @@ extern "C" int qb_window_attention_mma(const void* q, int dtype, const void* k_c
   P.num_pool_pages = num_pool_pages; P.scale = scale; P.cap = cap; P.window = window; P.pool = pool;
   P.dist_bias = dist_bias; P.sink = sink; P.all_values = talk != nullptr; P.status = status; P.vec = 1;
   P.n_split = 1; P.part = nullptr;
-  const size_t smem = ((size_t)(WM_BM + WM_BN) * (hd + 8) + (size_t)WM_BN * (vd + 8)) * 2 + 2 * WM_BM * sizeof(int);
+  const size_t smem = ((size_t)(WM_BM + 2 * WM_BN) * (hd + 8) + (size_t)2 * WM_BN * (vd + 8)) * 2 + 2 * WM_BN * sizeof(long long)
+                      + 4 * WM_BN * sizeof(float) + 2 * WM_BM * sizeof(int);
   dim3 grid((T + WM_BM - 1) / WM_BM, nq, P.all_values ? nkv : 1);
 #define QB_WM_LAUNCH(NTV)                                                                                         \
   do {                                                                                                            \
@@ -663,7 +915,7 @@ extern "C" int qb_window_attention_mma(const void* q, int dtype, const void* k_c
 #undef QB_WM_LAUNCH
   QB_LAUNCH_CHECK();
   if (talk != nullptr) {
-    talk_mix_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(scratch, talk, (__nv_bfloat16*)out, T, nq, nkv, vd);
+    talk_mix_kernel<__nv_bfloat16><<<T * nq, 128, 0, stream>>>(scratch, talk, (__nv_bfloat16*)out, T, nq, nkv, vd);
     QB_LAUNCH_CHECK();
   }
   return 0;

@@ -893,8 +893,8 @@ def window_attention(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, sc
             _stream()), "window_attention_mma", 1 + (talk is not None))
         return
     if n_split is None:
-        warps = T * nq
-        n_split = 1 if (warps >= 1024 or window <= 0) else max(1, min(-(-2048 // warps), -(-window // 64), 64))
+        warps = T * nkv * (nkv if talk is not None else 1)        # of the kernel that shares a key row among q heads
+        n_split = 1 if window <= 0 else max(1, min(-(-8192 // warps), -(-window // 32), 64))
     part = None
     if n_split > 1:
         part = torch.empty(T * nq * n_split * (2 + (nkv if talk is not None else 1) * vd), dtype=torch.float32,
@@ -925,22 +925,21 @@ def pool_blocks(k_cache, v_cache, pooled_k, pooled_v, tok_pos, tok_req, block_ta
 SCAN_MAX_STATE = 256
 
 
-def selective_scan(u, proj, z, w_dt, dt_bias, A, D, state, out, req_start, req_slot, rank: int, n_state: int) -> None:
+def selective_scan(u, proj, z, dt_pre, dt_bias, A, D, state, out, req_start, req_slot, rank: int, n_state: int) -> None:
     """``S <- exp(dt A) S + dt u B``, ``y = S C + D u``, ``out = y * silu(z)`` per channel over each request's rows, with
-    ``dt = softplus(w_dt low + dt_bias)``.  ``u`` ``[T, inner]`` in the activation dtype; ``proj`` float32 rows
+    ``dt = softplus(dt_pre + dt_bias)``.  ``u`` ``[T, inner]`` in the activation dtype; ``proj`` float32 rows
     ``[low (rank) | B (n_state) | C (n_state)]``; ``z`` float32 ``[T, inner]`` (a column range of wider rows is fine);
-    ``w_dt`` float32 ``[rank, inner]`` (the step projection, transposed); ``A`` float32 ``[inner, n_state]`` (negative); ``state`` float32
-    ``[slots, inner, n_state]``, read and left updated at the rows ``req_slot``."""
+    ``dt_pre`` float32 ``[T, inner]``, the step projection of ``low``; ``A`` float32 ``[inner, n_state]`` (negative);
+    ``state`` float32 ``[slots, inner, n_state]``, read and left updated at the rows ``req_slot``."""
     T, inner = u.shape
-    for t, n in ((proj, "proj"), (z, "z"), (w_dt, "w_dt"), (dt_bias, "dt_bias"), (A, "A"), (D, "D"), (state, "state")):
+    for t, n in ((proj, "proj"), (z, "z"), (dt_pre, "dt_pre"), (dt_bias, "dt_bias"), (A, "A"), (D, "D"), (state, "state")):
         _want(t, torch.float32, n)
     if (proj.shape[0] != T or proj.shape[1] < rank + 2 * n_state or proj.stride(1) != 1 or tuple(z.shape) != (T, inner)
-            or z.stride(1) != 1 or tuple(w_dt.shape) != (rank, inner) or tuple(A.shape) != (inner, n_state)
-            or D.numel() != inner or dt_bias.numel() != inner or tuple(state.shape[1:]) != (inner, n_state)
-            or tuple(out.shape) != (T, inner) or out.dtype != u.dtype):
+            or z.stride(1) != 1 or tuple(dt_pre.shape) != (T, inner) or not dt_pre.is_contiguous()
+            or tuple(A.shape) != (inner, n_state) or D.numel() != inner or dt_bias.numel() != inner
+            or tuple(state.shape[1:]) != (inner, n_state) or tuple(out.shape) != (T, inner) or out.dtype != u.dtype):
         raise ValueError("selective_scan: shape mismatch")
-    dt = torch.empty((T, inner), dtype=torch.float32, device=u.device)
     _check(lib().qb_selective_scan(_p(u), _code(u), ctypes.c_void_p(proj.data_ptr()), int(proj.stride(0)),
-                                   ctypes.c_void_p(z.data_ptr()), int(z.stride(0)), _p(w_dt), _p(dt_bias), _p(A), _p(D),
-                                   _p(state), _p(dt), _p(out), _p(req_start), _p(req_slot), T, req_slot.numel(), inner,
-                                   int(n_state), int(rank), _stream()), "selective_scan", 2)
+                                   ctypes.c_void_p(z.data_ptr()), int(z.stride(0)), _p(dt_pre), _p(dt_bias), _p(A), _p(D),
+                                   _p(state), _p(out), _p(req_start), _p(req_slot), T, req_slot.numel(), inner,
+                                   int(n_state), int(rank), _stream()), "selective_scan")

@@ -7,8 +7,9 @@ channel with a bias and silu; ``[low | B | C] = W_x u`` (``dt_rank``, ``state``,
     S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n          y_c = sum_n S[c, n] C_n + D_c u_c
 
 then ``y * silu(z)`` and ``W_o``.  ``S`` (float32, zero at admission) and the convolution's last ``taps - 1``
-inputs are per-request state.  Step sizes, decays, the state and the gate are float32; the three projections
-are library products whose float32 accumulators feed the kernels.
+inputs are per-request state.  Step sizes, decays, the state and the gate are float32; the projections are
+library products whose float32 accumulators feed the kernels (the step projection multiplies the float32 ``low``
+with the float32 copy of ``W_dt``; its bias and softplus are applied inside the scan).
 
 ``parallel_mixers``: two mixers read the same input; the result is ``left_scale * left + right_scale * right``.
 Their caches and states live side by side (stream and state names must differ); the sum is left to the norm
@@ -56,7 +57,7 @@ class SelectiveScan(Mixer):
         rows = -(-w_x.shape[0] // 8) * 8               # product rows that start on 16 bytes
         self.w_x = torch.zeros((rows, self.inner), dtype=w_x.dtype, device=w_x.device)
         self.w_x[: w_x.shape[0]].copy_(w_x)
-        self.w_dt, self.dt_b = fetch(n["dt"]).t().contiguous(), fetch(n["dt_b"]).contiguous()    # [dt_rank, inner]
+        self.w_dt, self.dt_b = fetch(n["dt"]).contiguous(), fetch(n["dt_b"]).contiguous()
         self.A = (-torch.exp(fetch(n["A_log"]).float())).contiguous()
         self.D, self.w_o = fetch(n["D"]).contiguous(), fetch(n["o"])
 
@@ -72,7 +73,8 @@ class SelectiveScan(Mixer):
                            ctx.req_slot, bias=self.conv_b, silu=True)
         proj = linear(u, self.w_x, out_dtype=torch.float32)
         y = empty_rows(T, C, dtype=x.dtype, device=x.device)
-        kernels.selective_scan(u, proj, uz[:, C:], self.w_dt, self.dt_b, self.A, self.D, state[self.state_name], y,
+        dt_pre = linear(proj[:, : self.R], self.w_dt)          # float32 operands: a true float32 product
+        kernels.selective_scan(u, proj, uz[:, C:], dt_pre, self.dt_b, self.A, self.D, state[self.state_name], y,
                                ctx.req_start, ctx.req_slot, self.R, self.N)
         return linear(y, self.w_o, out_dtype=torch.float32)
 
