@@ -23,11 +23,14 @@ constexpr int SS_CH = 16;              // channels a block
 constexpr int SS_MAX_STATE = 256;
 
 __device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ void ss_copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" :: "r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
 
 // NPL: states a lane holds, N <= 8 * NPL.  The request's rows are walked in chunks of `tok` tokens: the block first
-// brings the chunk's step sizes, inputs and B / C vectors into shared memory (all threads, whole segments of the
-// rows), then every lane runs the chunk's steps from there (nothing in the chain waits for global memory), then
-// the block gates and writes the chunk's outputs.
+// brings the chunk's step sizes, inputs, gates and B / C vectors into shared memory (asynchronous copies that run
+// while the chunk before is computed), then every lane runs the chunk's steps from there (nothing in the chain
+// waits for global memory), then the block gates and writes the chunk's outputs.
 template <typename U, typename O, int NPL>
 __global__ void __launch_bounds__(SS_CH * SS_LANES)
 scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt_pre, const float* __restrict__ dt_bias,
@@ -37,11 +40,11 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt_pre, con
                   O* __restrict__ out, const int* __restrict__ req_start, const int* __restrict__ req_slot, int inner,
                   int N, int tok) {
   extern __shared__ float ss_smem[];
-  float* s_dt = ss_smem;                        // [tok][SS_CH]
-  float* s_u = s_dt + tok * SS_CH;              // [tok][SS_CH]
+  // two buffers of what the copies bring (step projections -> step sizes, gates, B and C vectors), one of the
+  // inputs and one of the sums
+  const int buf_floats = tok * (2 * SS_CH + 2 * N);
+  float* s_u = ss_smem + 2 * buf_floats;        // [tok][SS_CH]
   float* s_y = s_u + tok * SS_CH;               // [tok][SS_CH]
-  float* s_B = s_y + tok * SS_CH;               // [tok][N]
-  float* s_C = s_B + tok * N;                   // [tok][N]
   const int r = blockIdx.y;
   const int first = req_start[r], last = req_start[r + 1];
   if (last <= first) return;
@@ -59,20 +62,56 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt_pre, con
     a[i] = n < N ? A[(size_t)cc * N + n] : 0.f;
   }
   const float d_c = D[cc];
-  for (int t0 = first; t0 < last; t0 += tok) {
-    const int nt = min(tok, last - t0);
+  // a chunk's rows travel by 4-byte asynchronous copies while the chunk before it is computed and written
+  auto start_copies = [&](int t0, int nt, int buf) {
+    float* b_dt = ss_smem + buf * buf_floats;
+    float* b_z = b_dt + tok * SS_CH;
+    float* b_B = b_z + tok * SS_CH;
+    float* b_C = b_B + tok * N;
     for (int i = threadIdx.x; i < nt * SS_CH; i += blockDim.x) {
       const int tt = i / SS_CH, k = min(c0 + i % SS_CH, inner - 1);
-      s_dt[i] = ss_softplus(dt_pre[(size_t)(t0 + tt) * inner + k] + dt_bias[k]);
-      s_u[i] = qb_to_float<U>(u[(size_t)(t0 + tt) * inner + k]);
+      ss_copy4(b_dt + i, dt_pre + (size_t)(t0 + tt) * inner + k);
+      ss_copy4(b_z + i, z + (size_t)(t0 + tt) * z_stride + k);
     }
     for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
       const int tt = i / N, n = i % N;
       const float* row = proj + (size_t)(t0 + tt) * proj_stride;
-      s_B[i] = row[b_off + n];
-      s_C[i] = row[c_off + n];
+      ss_copy4(b_B + i, row + b_off + n);
+      ss_copy4(b_C + i, row + c_off + n);
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  constexpr int UR = 32 * SS_CH / (SS_CH * SS_LANES);       // inputs of a chunk a thread carries (tok <= 32)
+  float ur[UR];
+  auto fetch_inputs = [&](int t0, int nt) {
+#pragma unroll
+    for (int j = 0; j < UR; ++j) {
+      const int i = threadIdx.x + j * SS_CH * SS_LANES;
+      ur[j] = i < nt * SS_CH ? qb_to_float<U>(u[(size_t)(t0 + i / SS_CH) * inner + min(c0 + i % SS_CH, inner - 1)]) : 0.f;
+    }
+  };
+  start_copies(first, min(tok, last - first), 0);
+  fetch_inputs(first, min(tok, last - first));
+  int buf = 0;
+  for (int t0 = first; t0 < last; t0 += tok, buf ^= 1) {
+    const int nt = min(tok, last - t0);
+    float* s_dt = ss_smem + buf * buf_floats;
+    const float* s_z = s_dt + tok * SS_CH;
+    const float* s_B = s_z + tok * SS_CH;
+    const float* s_C = s_B + tok * N;
+#pragma unroll
+    for (int j = 0; j < UR; ++j) {
+      const int i = threadIdx.x + j * SS_CH * SS_LANES;
+      if (i < nt * SS_CH) s_u[i] = ur[j];
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    for (int i = threadIdx.x; i < nt * SS_CH; i += blockDim.x)      // the thread's own copies: step sizes from them
+      s_dt[i] = ss_softplus(s_dt[i] + dt_bias[min(c0 + i % SS_CH, inner - 1)]);
+    __syncthreads();                  // the chunk is there, and the chunk before it has been written out by all
+    if (t0 + tok < last) {
+      start_copies(t0 + tok, min(tok, last - t0 - tok), buf ^ 1);
+      fetch_inputs(t0 + tok, min(tok, last - t0 - tok));
+    }
     // U steps at a time: their decays, inputs and output vectors are formed first (nothing of that waits for the
     // state), then the state walks through them, then the U sums are added up across the lanes side by side
     constexpr int U = NPL <= 4 ? 4 : NPL <= 8 ? 2 : 1;
@@ -116,12 +155,10 @@ scan_chain_kernel(const U* __restrict__ u, const float* __restrict__ dt_pre, con
     for (int i = threadIdx.x; i < nt * SS_CH; i += blockDim.x) {
       const int tt = i / SS_CH, k = c0 + i % SS_CH;
       if (k < inner) {
-        const float zv = z[(size_t)(t0 + tt) * z_stride + k];
+        const float zv = s_z[i];
         out[(size_t)(t0 + tt) * inner + k] = qb_from_float<O>(s_y[i] * (zv / (1.f + expf(-zv))));
       }
     }
-    // the next chunk's loads write s_dt / s_u / s_B / s_C, which no thread reads any more, and s_y only after the
-    // barrier that follows them
   }
   if (live) {
 #pragma unroll
@@ -145,7 +182,7 @@ extern "C" int qb_selective_scan(const void* u, int dtype, const float* proj, in
   if (N > SS_MAX_STATE || R_req > 65535) return QB_ERR_UNSUPPORTED;
   dim3 grid((inner + SS_CH - 1) / SS_CH, R_req);
   // tokens a chunk: at most 32, at most the longest portion can be, and what 44 KB of shared memory hold
-  const int per_tok = (3 * SS_CH + 2 * N) * (int)sizeof(float);
+  const int per_tok = (2 * (2 * SS_CH + 2 * N) + 2 * SS_CH) * (int)sizeof(float);      // two buffers, inputs, sums
   int tok = 44 * 1024 / per_tok;
   tok = tok > 32 ? 32 : tok;
   tok = tok > T ? T : tok;

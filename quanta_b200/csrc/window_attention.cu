@@ -501,8 +501,8 @@ extern "C" int qb_window_attention(const void* q, int dtype, const void* k_cache
 // ---------------------------------------------------------------------------------------------
 // Pooled blocks: a token whose position ends a block of `pool` tokens (pos % pool == pool - 1) leaves the mean of
 // the block's keys and the mean of its values, as the cache holds them, in row pos / pool of the pooled pages.
-// The block's earlier tokens may have come in earlier steps: they are read from the pages.  One block per token;
-// sums in position order, float32.
+// The block's earlier tokens may have come in earlier steps: they are read from the pages.  Blocks of 128 elements
+// per token; sums in position order, float32.
 // ---------------------------------------------------------------------------------------------
 template <typename A>
 __global__ void pool_blocks_kernel(const A* __restrict__ k_cache, const A* __restrict__ v_cache,
@@ -523,20 +523,31 @@ __global__ void pool_blocks_kernel(const A* __restrict__ k_cache, const A* __res
   }
   const float inv = 1.f / (float)pool;
   const int kn = nkv * hd, vn = nkv * vd;
-  for (int i = threadIdx.x; i < kn + vn; i += blockDim.x) {
-    const bool is_k = i < kn;
-    const int j = is_k ? i : i - kn, w = is_k ? hd : vd;
-    const int head = j / w, d = j % w;
-    const A* src = is_k ? k_cache : v_cache;
-    float sum = 0.f;
-    for (int p = pos - pool + 1; p <= pos; ++p) {
-      const int page = bt[p / page_size];
-      if (page < 0 || page >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, page, 2); continue; }
-      sum += qb_to_float<A>(src[(((size_t)page * nkv + head) * page_size + p % page_size) * w + d]);
+  // a thread an element; eight positions are asked for before the first is added (few blocks have work)
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= kn + vn) return;
+  const bool is_k = i < kn;
+  const int j = is_k ? i : i - kn, w = is_k ? hd : vd;
+  const int head = j / w, d = j % w;
+  const A* src = is_k ? k_cache : v_cache;
+  float sum = 0.f;
+  for (int p0 = pos - pool + 1; p0 <= pos; p0 += 8) {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int p = p0 + u;
+      x[u] = 0.f;
+      if (p <= pos) {
+        const int page = bt[p / page_size];
+        if (page < 0 || page >= num_pages) qb_set_status(status, QB_STATUS_BAD_PAGE, page, 2);
+        else x[u] = qb_to_float<A>(src[(((size_t)page * nkv + head) * page_size + p % page_size) * w + d]);
+      }
     }
-    A* dst = is_k ? kp_cache : vp_cache;
-    dst[(((size_t)dst_page * nkv + head) * page_size + b % page_size) * w + d] = qb_from_float<A>(sum * inv);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) sum += x[u];
   }
+  A* dst = is_k ? kp_cache : vp_cache;
+  dst[(((size_t)dst_page * nkv + head) * page_size + b % page_size) * w + d] = qb_from_float<A>(sum * inv);
 }
 
 extern "C" int qb_pool_blocks(const void* k_cache, const void* v_cache, void* kp_cache, void* vp_cache, int dtype,
@@ -545,7 +556,8 @@ extern "C" int qb_pool_blocks(const void* k_cache, const void* v_cache, void* kp
                               int num_pages, int num_pool_pages, int pool, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (pool <= 0 || page_size <= 0 || nkv <= 0 || hd <= 0 || vd <= 0) return QB_ERR_BAD_ARG;
-  QB_DISPATCH_DTYPE(dtype, A, pool_blocks_kernel<A><<<T, 128, 0, stream>>>(
+  const dim3 grid(T, (nkv * (hd + vd) + 127) / 128);
+  QB_DISPATCH_DTYPE(dtype, A, pool_blocks_kernel<A><<<grid, 128, 0, stream>>>(
       (const A*)k_cache, (const A*)v_cache, (A*)kp_cache, (A*)vp_cache, tok_pos, tok_req, block_table, bt_stride,
       pool_table, pool_stride, T, nkv, hd, vd, page_size, num_pages, num_pool_pages, pool, status));
   QB_LAUNCH_CHECK();
