@@ -28,7 +28,7 @@ __global__ void short_conv_rows_kernel(const float* __restrict__ x, const float*
   const int first = req_start[r];
   const int hist = taps - 1;
   const float* st = state + (size_t)req_slot[r] * hist * C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += blockDim.x * gridDim.y) {
     const float cur = x[(size_t)t * x_stride + c];
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {
@@ -59,7 +59,7 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, float* __re
   float* st = state + (size_t)req_slot[r] * hist * C;
   // a thread owns its channels in every state row, so the shift needs no barrier: new row i is the input
   // n - hist + i of the step when that is >= 0, else old row i + n
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += blockDim.x * gridDim.y) {
     for (int i = 0; i < hist; ++i) {
       const int src = n - hist + i;
       st[(size_t)i * C + c] = src >= 0 ? x[(size_t)(first + src) * x_stride + c] : st[(size_t)(i + n) * C + c];
@@ -73,11 +73,15 @@ extern "C" int qb_short_conv(const float* x, const float* w, float* state, void*
   if (T <= 0) return 0;
   if (taps < 1 || C <= 0 || x_stride < C || (act != 0 && act != 1)) return QB_ERR_BAD_ARG;
   const int threads = C >= 1024 ? 256 : 128;
-  QB_DISPATCH_DTYPE(out_dtype, O, short_conv_rows_kernel<O><<<T, threads, 0, stream>>>(
+  // a step of few rows spreads a row's channels over several blocks (a thread a channel): with one block a row
+  // such a step is as long as its longest chain of loads
+  const int parts = T >= 512 ? 1 : min(64, (C + threads - 1) / threads);
+  QB_DISPATCH_DTYPE(out_dtype, O, short_conv_rows_kernel<O><<<dim3(T, parts), threads, 0, stream>>>(
       x, w, state, (O*)out, tok_req, req_start, req_slot, T, C, taps, x_stride, bias, act));
   QB_LAUNCH_CHECK();
   if (taps > 1) {
-    short_conv_state_kernel<<<R, threads, 0, stream>>>(x, state, req_start, req_slot, R, C, taps, x_stride);
+    short_conv_state_kernel<<<dim3(R, min(64, (C + threads - 1) / threads)), threads, 0, stream>>>(x, state, req_start, req_slot,
+                                                                                                 R, C, taps, x_stride);
     QB_LAUNCH_CHECK();
   }
   return 0;
