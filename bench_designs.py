@@ -98,12 +98,12 @@ def tarulix_raw(s: dict) -> dict:
     heads = {"heads": s["attn_heads"], "kv_heads": max(1, s["attn_heads"] // 4), "dim": s["dim"], "vdim": s["dim"],
              "scale": 1.0 / math.sqrt(s["dim"])}
     attn = dict(heads, mask={"size": s["window"]}, bias_max=4 * s["window"], v_mix=True)
-    left = dict(heads, mask={"size": s["window"], "pool": s["pool"]}, rot={"dims": s["rot"], "base": 1e6}, softcap=30.0)
+    left = dict(heads, mask={"size": s["window"], "pool": s["pool"]}, rot={"dims": s["rot"], "base": 5e5}, softcap=20.0)
     right = {"inner": s["inner"], "state": s["state"], "dt_rank": s["dt_rank"], "conv": s["taps"]}
     layers = []
     for _ in range(s["groups"]):
         layers += [{"type": "attention", "mixer": dict(attn), "mlp": moe}, {"type": "attention", "mixer": dict(attn), "mlp": moe},
-                   {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right), "left_scale": 0.8, "right_scale": 0.9},
+                   {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right), "left_scale": 0.75, "right_scale": 1.1},
                     "mlp": moe}]
     return {"architecture": "Tarulix", "vocab": s["vocab"], "width": s["width"], "layers": layers, "norm": {"eps": 1e-5}}
 
@@ -361,7 +361,7 @@ def window_attn(tokens_per_req: int, reqs: int, context: int, nq: int, nkv: int,
     else:
         rows = -(-context // pool)
         ppp = -(-rows // page)
-        extras = dict(softcap=30.0, pool=pool, pooled_k=torch.randn(reqs * ppp, nkv, page, hd, device=dev, dtype=torch.bfloat16),
+        extras = dict(softcap=20.0, pool=pool, pooled_k=torch.randn(reqs * ppp, nkv, page, hd, device=dev, dtype=torch.bfloat16),
                       pooled_v=torch.randn(reqs * ppp, nkv, page, hd, device=dev, dtype=torch.bfloat16),
                       pool_table=torch.randperm(reqs * ppp, dtype=torch.int32).view(reqs, ppp).to(dev),
                       talk=torch.eye(nq, device=dev) + 0.1 * torch.randn(nq, nq, device=dev),

@@ -26,7 +26,7 @@ def _attn(heads, kv_heads, dim, vdim, window, far, rows, v_mix=True, scale=None,
     return {"type": "attention", "mixer": m, "mlp": mlp}
 
 
-def _par(heads, kv_heads, dim, vdim, window, pool, rot, cap, inner, state, rank, taps, weights=(0.8, 0.9), mlp=None, scale=None):
+def _par(heads, kv_heads, dim, vdim, window, pool, rot, cap, inner, state, rank, taps, weights=(0.75, 1.1), mlp=None, scale=None):
     left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale or 1.0 / math.sqrt(dim),
             "mask": {"size": window, "pool": pool}, "softcap": cap}
     if rot is not None:
@@ -67,8 +67,8 @@ CONFIGS = {
         _attn(6, 1, 16, 16, 6, 9, 6),
         _attn(2, 2, 40, 8, 23, 24, 2, v_mix=False, mlp=_moe(1, 1, 1, 8, 0))], eps=1e-6),
     "C": _config(61, 44, [
-        _par(3, 3, 12, 20, 13, 7, (4, 100.0), 30.0, 20, 24, 5, 3, (0.5, 1.5), mlp=_moe(9, 4, 4, 8, 12)),
-        _par(2, 1, 20, 12, 300, 4, (20, 1e6), 0.0, 36, 3, 1, 4, (1.0, 1.0)),
+        _par(3, 3, 12, 20, 13, 7, (4, 100.0), 25.0, 20, 24, 5, 3, (0.5, 1.5), mlp=_moe(9, 4, 4, 8, 12)),
+        _par(2, 1, 20, 12, 300, 4, (20, 2e5), 0.0, 36, 3, 1, 4, (1.0, 1.0)),
         _attn(1, 1, 24, 24, 31, 100, 10, mlp=_moe(3, 1, 2, 16, 0))], eps=1e-4),
     # shapes that the tensor-core products take in bfloat16: widths and expert sizes that are multiples of 8, heads
     # of 64 and 128
