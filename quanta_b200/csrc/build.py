@@ -31,10 +31,10 @@ from pathlib import Path
 SRC_DIR = Path(__file__).resolve().parent
 # unit -> its sources.  A file that calls into another one is in the same unit.
 UNITS = {
-    "core": ["norm_embed.cu", "sampling.cu"],
+    "core": ["norm_embed.cu", "grouped_norm.cu", "sampling.cu"],
     "attention": ["rope_cache.cu", "attention_simt.cu", "attention_mma.cu", "attention_tc.cu"],
     "experts": ["moe.cu", "router_gemm_mma.cu", "expert_gemm_tc.cu"],
-    "recurrent": ["short_conv.cu", "delta_rule.cu"],
+    "recurrent": ["short_conv.cu", "delta_rule.cu", "gated_delta.cu"],
     "latent": ["latent_attention.cu"],
     "linear_attention": ["gla.cu"],
     "window_attention": ["window_attention.cu"],

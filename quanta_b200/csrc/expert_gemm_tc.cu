@@ -11,7 +11,8 @@
 //   warp 1   : MMA issuer.  4 x tcgen05.mma (K = 16 each) per stage and matrix, D[128 x NT] float32 in
 //              TMEM; tcgen05.commit frees the stage and, at the end, signals the epilogue.
 //   warps 2-5: epilogue (2-9 in the blocks of a pair).  tcgen05.ld (one TMEM lane = one output feature per thread), then
-//              MODE 1: act[p, j] = silu(gate) * up  (bfloat16),  gate/up = two accumulators;
+//              MODE 1: act[p, j] = silu(gate) * up  (bfloat16),  gate/up = two accumulators; or, with the
+//              clamped activation (EgAct), the routing weight applied to both accumulators first;
 //              MODE 2: y[pair(p), n] = w[pair(p)] * acc  (float32);
 //              MODE 3: act[p, j] = relu(acc)^2  (bfloat16): the first product of ungated experts, whose weights
 //              are one matrix [E, I, K] (token rows fetched as in MODE 1, weight tiles laid out as in MODE 2).
@@ -162,6 +163,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // silu(g) * u.  The exponential and the quotient are the fast ones (2 ulp); the result is rounded to bfloat16.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
+// The activation of a gated first product (MODE 1).  kind 0: silu(gate) * up.  kind 1: the row's routing weight w
+// multiplies both accumulators first (the expert reads w * x, and the products are linear in x), then
+// g = min(w gate, limit), u = clamp(w up, -limit, limit), g * sigmoid(alpha g) * (u + 1).
+struct EgAct {
+  int kind;
+  float limit, alpha;
+};
+__device__ __forceinline__ float clamped_glu(float g, float u, float w, const EgAct& a) {
+  g = fminf(g * w, a.limit);
+  u = fminf(fmaxf(u * w, -a.limit), a.limit);
+  return __fdividef(g, 1.f + __expf(-a.alpha * g)) * (u + 1.f);
+}
+
 struct EgShared {
   uint64_t full[8];
   uint64_t empty[8];
@@ -187,7 +201,7 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
                     void* __restrict__ out, const int* __restrict__ sorted_pair, const float* __restrict__ pair_w,
                     const int* __restrict__ plan, const int* __restrict__ tile_expert,
                     const int* __restrict__ tile_row0, int E, int K, int N_out, int NT, int stages,
-                    int tmem_cols, int gather_k, int* status) {
+                    int tmem_cols, int gather_k, int* status, EgAct act) {
   constexpr int FEATS = MODE == 1 ? EG_M : NM * EG_M;      // output features a block
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;     // 0: the block that issues the MMAs
   extern __shared__ unsigned char smem_dyn[];
@@ -352,13 +366,14 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
     constexpr int EPI_THREADS = SPLIT * 128;
     const int quad = warp & 3, sub = (warp - 2) >> 2;
     const int feat = j0 + quad * 32 + lane;
-    if (MODE == 2) {
+    if (MODE == 2 || (MODE == 1 && act.kind == 1)) {
       // where each row goes and its routing weight: fetched here, under the main loop, by the warps that
-      // need them at its end (two dependent reads that the producer and the issuer do not wait for)
+      // need them at its end (two dependent reads that the producer and the issuer do not wait for); no
+      // weights: every row counts once
       for (int i = threadIdx.x - 64; i < NT; i += EPI_THREADS) {
         const int pr = i < rows ? sorted_pair[row0 + i] : 0;
         s_pair[i] = pr;
-        s_w[i] = i < rows ? pair_w[pr] : 0.f;
+        s_w[i] = i < rows ? (pair_w != nullptr ? pair_w[pr] : 1.f) : 0.f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");      // the epilogue warps
     }
@@ -380,7 +395,7 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float g = __uint_as_float(v0[i]), u = __uint_as_float(v1[i]);
-            r[i] = __float2bfloat16_rn(silu_mul(g, u));
+            r[i] = __float2bfloat16_rn(act.kind == 1 ? clamped_glu(g, u, s_w[c0 + i], act) : silu_mul(g, u));
           }
           if (feat < N_out) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)(row0 + c0) * N_out + feat;
@@ -434,8 +449,8 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
   const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, void* __restrict__ out,     \
       const int* __restrict__ sorted_pair, const float* __restrict__ pair_w, const int* __restrict__ plan,        \
       const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int E, int K, int N_out, int NT,    \
-      int stages, int tmem_cols, int gather_k, int* status
-#define QB_EG_ARGS tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, N_out, NT, stages, tmem_cols, gather_k, status
+      int stages, int tmem_cols, int gather_k, int* status, EgAct act
+#define QB_EG_ARGS tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, N_out, NT, stages, tmem_cols, gather_k, status, act
 
 template <int MODE, int NM>
 __global__ void __launch_bounds__(EG_THREADS, 2) expert_gemm_tc_kernel(QB_EG_PARAMS) {
@@ -508,8 +523,11 @@ extern "C" int qb_gather_rows(const void* x, void* out, const int* sorted_pair, 
 extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weights, void* out, const int* sorted_pair,
                                  const float* pair_w, const int* plan, const int* tile_expert, const int* tile_row0,
                                  int max_tiles, int n_pairs, int E, int K, int N_out, int NT, int gather_k, int n_rows,
-                                 int* status, int weight_experts, cudaStream_t stream) {
+                                 int* status, int weight_experts, int act_kind, float act_limit, float act_alpha,
+                                 cudaStream_t stream) {
   if (max_tiles <= 0 || n_pairs <= 0) return 0;
+  if (act_kind < 0 || act_kind > 1 || (act_kind == 1 && (mode != 1 || pair_w == nullptr))) return QB_ERR_BAD_ARG;
+  const EgAct act{act_kind, act_limit, act_alpha};
   if (weight_experts <= 0 || weight_experts > E) weight_experts = E;
   if (K % 8 || K <= 0 || N_out <= 0 || NT < 16 || NT > 256 || NT % 16 || max_tiles > 65535) return QB_ERR_UNSUPPORTED;
   if (mode != 1 && mode != 2 && mode != 3) return QB_ERR_BAD_ARG;
@@ -564,7 +582,7 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
     err = cudaFuncSetAttribute(KERNEL_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
     if (err != cudaSuccess) return (int)err;                                                                       \
     KERNEL_<<<grid, THREADS_, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, \
-                                               N_out, NT, stages, tmem_cols, GK, status);                          \
+                                               N_out, NT, stages, tmem_cols, GK, status, act);                     \
   } while (0)
   if (pair && mode == 1) QB_EG(expert_gemm_tc_pair_kernel<1>, gather_k, EG_PAIR_THREADS);
   else if (pair && mode == 3) QB_EG(expert_gemm_tc_pair_kernel<3>, gather_k, EG_PAIR_THREADS);

@@ -656,7 +656,9 @@ extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan
 // ---------------------------------------------------------------------------------------------
 // grouped products, SIMT.  Tile = 32 sorted rows of one expert x 64 output features, k slices of 16.
 //   MODE 1: act[p, j]   = silu(x[tok(p)] . W13[e][j]) * (x[tok(p)] . W13[e][I + j]),  j < I
-//   MODE 2: y[pair(p), n] = w[pair(p)] * (act[p] . W2[e][n]),  n < H
+//           (act_kind 1: with g, u the two products times the pair's routing weight, g' = min(g, limit),
+//           u' = clamp(u, -limit, limit), act = g' * sigmoid(alpha g') * (u' + 1))
+//   MODE 2: y[pair(p), n] = w[pair(p)] * (act[p] . W2[e][n]),  n < H        (no weights given: w = 1)
 //   MODE 3: act[p, j]   = relu(x[tok(p)] . W1[e][j])^2,  j < I            (ungated experts; weights [E, I, K])
 // Each output is one sequential float32 sum over the inner dimension.
 // ---------------------------------------------------------------------------------------------
@@ -667,7 +669,8 @@ __global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __rest
                                         O* __restrict__ out, const int* __restrict__ sorted_pair,
                                         const float* __restrict__ pair_w, const int* __restrict__ plan,
                                         const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                                        int E, int top_k, int K, int N) {
+                                        int E, int top_k, int K, int N, int act_kind, float act_limit,
+                                        float act_alpha) {
   // MODE 1: K = hidden, N = I (weights [E, 2N, K]); MODE 2: K = I, N = hidden (weights [E, N, K]);
   // MODE 3: K = hidden, N = I (weights [E, N, K])
   const int* offsets = plan + 2 * E;
@@ -750,8 +753,16 @@ __global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __rest
       for (int j = 0; j < 4; ++j) {
         const int gn = n0 + tx * 4 + j;
         if (gn >= N) continue;
-        const float g = acc[0][i][j], u = acc[MODE == 1 ? 1 : 0][i][j];
-        out[(size_t)p * N + gn] = qb_from_float<O>(g / (1.f + expf(-g)) * u);
+        float g = acc[0][i][j], u = acc[MODE == 1 ? 1 : 0][i][j];
+        if (act_kind == 1) {
+          // the routing weight multiplies the expert's input, and so both products; clamps; g sigmoid(alpha g) (u + 1)
+          const float w = pair_w[sorted_pair[p]];
+          g = fminf(g * w, act_limit);
+          u = fminf(fmaxf(u * w, -act_limit), act_limit);
+          out[(size_t)p * N + gn] = qb_from_float<O>(g / (1.f + expf(-act_alpha * g)) * (u + 1.f));
+        } else {
+          out[(size_t)p * N + gn] = qb_from_float<O>(g / (1.f + expf(-g)) * u);
+        }
       }
     } else if (MODE == 3) {
 #pragma unroll
@@ -762,7 +773,7 @@ __global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __rest
       }
     } else {
       const int pair = sorted_pair[p];
-      const float w = pair_w[pair];
+      const float w = pair_w != nullptr ? pair_w[pair] : 1.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int gn = n0 + tx * 4 + j;
@@ -776,23 +787,25 @@ __global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __rest
 extern "C" int qb_moe_grouped_simt(int mode, const void* x, int x_dtype, const void* weights, int w_dtype,
                                    void* out, int out_dtype, const int* sorted_pair, const float* pair_w,
                                    const int* plan, const int* tile_expert, const int* tile_row0,
-                                   int max_tiles, int E, int top_k, int K, int N, cudaStream_t stream) {
+                                   int max_tiles, int E, int top_k, int K, int N, int act_kind, float act_limit,
+                                   float act_alpha, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
+  if (act_kind < 0 || act_kind > 1 || (act_kind == 1 && (mode != 1 || pair_w == nullptr))) return QB_ERR_BAD_ARG;
   if (max_tiles > 65535) return QB_ERR_UNSUPPORTED;
   dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
   QB_DISPATCH_DTYPE(x_dtype, X, QB_DISPATCH_DTYPE(w_dtype, W, QB_DISPATCH_DTYPE(out_dtype, O, {
     if (mode == 1)
       moe_grouped_simt_kernel<X, W, O, 1><<<grid, 256, 0, stream>>>(
           (const X*)x, (const W*)weights, (O*)out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E,
-          top_k, K, N);
+          top_k, K, N, act_kind, act_limit, act_alpha);
     else if (mode == 2)
       moe_grouped_simt_kernel<X, W, O, 2><<<grid, 256, 0, stream>>>(
           (const X*)x, (const W*)weights, (O*)out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E,
-          top_k, K, N);
+          top_k, K, N, act_kind, act_limit, act_alpha);
     else if (mode == 3)
       moe_grouped_simt_kernel<X, W, O, 3><<<grid, 256, 0, stream>>>(
           (const X*)x, (const W*)weights, (O*)out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E,
-          top_k, K, N);
+          top_k, K, N, act_kind, act_limit, act_alpha);
     else
       return QB_ERR_BAD_ARG;
   })));

@@ -9,6 +9,8 @@
 //            pair_axis[j] and angle float(pos) * inv_freq[j]  (src/quanta/minimax/model_m3.py:83-96)
 //   q     <- q * (1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1))     (temp_every > 0: a query
 //            temperature that grows with the position, float32)
+//   q     <- q * head_scale[head]          (head_scale: a float32 number per q head that multiplies the head's
+//            scores; null for none)
 //   v     <- (1 - lambda) v + lambda v_first      (v_first: float32 values [T, nkv * vd] that an earlier layer left for
 //            the same tokens, lambda one number on the device; v_export: this layer leaves its own values there)
 //   q     -> q_out [T, nq, hd];  k -> pages [page, kv_head, slot, hd], v -> pages [page, kv_head, slot, vd]
@@ -31,7 +33,7 @@ __global__ void qknorm_rope_write_kernel(
     const int* __restrict__ tok_req, const int* __restrict__ block_table, int bt_stride, int T, int nq,
     int nkv_all, int hd, int vd, int has_kv, int rd, float temp_coef, int temp_every, int page_size, int num_pages,
     int vec, const float* __restrict__ bias, const float* __restrict__ v_first, const float* __restrict__ v_lambda,
-    float* __restrict__ v_export, int* status) {
+    float* __restrict__ v_export, const float* __restrict__ head_scale, int* status) {
   extern __shared__ float smem[];
   const int t = blockIdx.x;
   if (t >= T) return;
@@ -153,12 +155,14 @@ __global__ void qknorm_rope_write_kernel(
     for (int c = threadIdx.x; c < qn / 8; c += blockDim.x) {
       float v[8];
       QbVec8<float>::load(buf + c * 8, v);
+      const float m = head_scale != nullptr ? temp * head_scale[c * 8 / hd] : temp;     // hd % 8 == 0 here
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] *= temp;
+      for (int e = 0; e < 8; ++e) v[e] *= m;
       QbVec8<A>::store(qo + c * 8, v);
     }
   } else {
-    for (int i = threadIdx.x; i < qn; i += blockDim.x) qo[i] = qb_from_float<A>(buf[i] * temp);
+    for (int i = threadIdx.x; i < qn; i += blockDim.x)
+      qo[i] = qb_from_float<A>(buf[i] * (head_scale != nullptr ? temp * head_scale[i / hd] : temp));
   }
 
   if (k_cache == nullptr) return;
@@ -216,7 +220,7 @@ extern "C" int qb_qknorm_rope_write(
     const int* positions, int n_axes, const int* tok_pos, const int* tok_req, const int* block_table,
     int bt_stride, int T, int nq, int nkv, int hd, int vd, int has_kv, int rd, float temp_coef, int temp_every,
     int page_size, int num_pages, const float* bias, const float* v_first, const float* v_lambda, float* v_export,
-    int* status, cudaStream_t stream) {
+    const float* head_scale, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rd % 2 || rd > hd || rd < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || hd <= 0 || vd <= 0) return QB_ERR_BAD_ARG;
   // a norm over the whole row needs gains; a per-head norm may have none (both null)
@@ -243,7 +247,7 @@ extern "C" int qb_qknorm_rope_write(
                                        k_norm_w, norm_kind, eps, inv_freq, pair_axis, positions, n_axes, tok_pos, \
                                        tok_req, block_table, bt_stride, T, nq, nkv, hd, vd, has_kv, rd, temp_coef, \
                                        temp_every, page_size, num_pages, vec, bias, v_first, v_lambda, v_export,  \
-                                       status);                                                                 \
+                                       head_scale, status);                                                              \
   } while (0)
   // steps of few tokens: more threads a token, so that each of the kernel's phases is short
   const int threads = T <= 64 ? 1024 : 256;

@@ -2,6 +2,7 @@
 //
 //   y_t = x_t + sum_{j < taps} w[:, j] * x_{t - taps + 1 + j}          (act 0: the input added back)
 //   y_t = silu(b + sum_{j < taps} w[:, j] * x_{t - taps + 1 + j})      (act 1: a bias and silu, nothing added back)
+//   y_t = sum_{j < taps} w[:, j] * x_{t - taps + 1 + j}                (act 2: the sum alone)
 //
 // with zeros before a sequence's start.  The rows of x may be a column range of wider rows (x_stride).
 //
@@ -42,6 +43,8 @@ __global__ void short_conv_rows_kernel(const float* __restrict__ x, const float*
     if (act == 1) {
       acc += bias != nullptr ? bias[c] : 0.f;
       out[(size_t)t * C + c] = qb_from_float<O>(acc / (1.f + expf(-acc)));
+    } else if (act == 2) {
+      out[(size_t)t * C + c] = qb_from_float<O>(acc);
     } else {
       out[(size_t)t * C + c] = qb_from_float<O>(cur + acc);
     }
@@ -71,7 +74,7 @@ extern "C" int qb_short_conv(const float* x, const float* w, float* state, void*
                              const int* tok_req, const int* req_start, const int* req_slot, int T, int R,
                              int C, int taps, int x_stride, const float* bias, int act, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (taps < 1 || C <= 0 || x_stride < C || (act != 0 && act != 1)) return QB_ERR_BAD_ARG;
+  if (taps < 1 || C <= 0 || x_stride < C || act < 0 || act > 2) return QB_ERR_BAD_ARG;
   const int threads = C >= 1024 ? 256 : 128;
   // a step of few rows spreads a row's channels over several blocks (a thread a channel): with one block a row
   // such a step is as long as its longest chain of loads

@@ -273,7 +273,7 @@ def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kin
                       inv_freq, pair_axis, positions, tok_pos, tok_req, block_table, nq: int, nkv: int,
                       hd: int, rd: int, page_size: int, status, *, vd: int | None = None, has_kv: bool = True,
                       q_temp_coef: float = 0.0, q_temp_every: int = 0, bias=None, v_first=None, v_lambda=None,
-                      v_export=None) -> None:
+                      v_export=None, head_scale=None) -> None:
     """Rows ``[q | k | v | ...]`` of a fused projection (``qkv`` may be wider than the three; its row stride is
     honoured) -> normed, rotated queries in ``q_out`` and keys / values in the pages.  ``vd``: the values' head
     size when it differs from ``hd``; ``has_kv`` False: the rows start with q alone (a layer that reads another
@@ -282,7 +282,8 @@ def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kin
     bfloat16.  ``bias``: float32, added to the row's ``[q | k | v]`` first.  A per-head norm may come without gains
     (both None).  ``v_first`` (float32 ``[T, nkv * vd]``) with ``v_lambda`` (one float32 on the device): the values
     become ``(1 - lambda) v + lambda v_first`` before they are cached; ``v_export``: this layer's own values (bias
-    added, not blended) are left there as float32."""
+    added, not blended) are left there as float32.  ``head_scale`` (float32 ``[nq]``): a number per q head that
+    multiplies the head's queries (and so its scores) after norm and rotation."""
     T = qkv.shape[0]
     vd = hd if vd is None else int(vd)
     if qkv.stride(1) != 1 or qkv.shape[1] < nq * hd + (nkv * (hd + vd) if has_kv else 0):
@@ -301,7 +302,7 @@ def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kin
         num_pages = k_cache.shape[0]
     n_row = nq * hd + (nkv * (hd + vd) if has_kv else 0)
     for t, n, size in ((bias, "bias", n_row), (v_first, "v_first", T * nkv * vd), (v_lambda, "v_lambda", 1),
-                       (v_export, "v_export", T * nkv * vd)):
+                       (v_export, "v_export", T * nkv * vd), (head_scale, "head_scale", nq)):
         if t is not None:
             _want(t, torch.float32, n)
             if t.numel() != size:
@@ -325,8 +326,8 @@ def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kin
         _p(q_norm_w), _p(k_norm_w) if has_kv else ctypes.c_void_p(0), norm_kind,
         ctypes.c_float(eps), _p(inv_freq), _p(pair_axis), _p(positions), n_axes, _p(tok_pos), _p(tok_req),
         _p(block_table), block_table.shape[1], T, nq, nkv, hd, vd, int(has_kv), rd, ctypes.c_float(q_temp_coef),
-        int(q_temp_every), page_size, num_pages, _p(bias), _p(v_first), _p(v_lambda), _p(v_export), _p(status),
-        _stream()), "qknorm_rope_write")
+        int(q_temp_every), page_size, num_pages, _p(bias), _p(v_first), _p(v_lambda), _p(v_export), _p(head_scale),
+        _p(status), _stream()), "qknorm_rope_write")
 
 
 def paged_attention_simt(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, scale: float,
@@ -511,12 +512,17 @@ def identity_slots(x, idx, w, y, first_identity: int) -> None:
            "identity_slots")
 
 
+EXPERT_ACT_SILU, EXPERT_ACT_CLAMPED = 0, 1
+
+
 def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
-                     n_experts: int, top_k: int) -> None:
+                     n_experts: int, top_k: int, act: tuple = (0, 0.0, 1.0)) -> None:
     """mode 1: ``out[p, :I] = silu(x[tok] W13_e[:I]^T) * (x[tok] W13_e[I:]^T)``; mode 2:
     ``out[pair] = w[pair] * (x[p] W2_e^T)``; mode 3: ``out[p] = relu(x[tok] W1_e^T)^2`` (ungated experts);
     rows p sorted by expert (see ``moe_plan``).  ``weights`` may hold fewer experts than the plan counts when the
-    plan gives the others no tiles."""
+    plan gives the others no tiles.  ``act`` = (kind, limit, alpha) for mode 1: ``EXPERT_ACT_CLAMPED`` multiplies both
+    products by the pair's routing weight first (the expert reads ``w * x``), then ``g = min(gate, limit)``,
+    ``u = clamp(up, -limit, limit)``, ``g * sigmoid(alpha g) * (u + 1)``.  Mode 2 with ``pair_w`` None: no weights."""
     K = x.shape[1]
     N = out.shape[1]
     want = (2 * N, K) if mode == 1 else (N, K)
@@ -524,7 +530,8 @@ def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile
         raise ValueError(f"moe_grouped: weights {tuple(weights.shape)} do not fit {n_experts} experts of {want}")
     _check(lib().qb_moe_grouped_simt(mode, _p(x), _code(x), _p(weights), _code(weights), _p(out), _code(out),
                                      _p(sorted_pair), _p(pair_w), _p(plan), _p(tile_expert), _p(tile_row0),
-                                     tile_expert.numel(), n_experts, top_k, K, N, _stream()), "moe_grouped_simt")
+                                     tile_expert.numel(), n_experts, top_k, K, N, int(act[0]), ctypes.c_float(act[1]),
+                                     ctypes.c_float(act[2]), _stream()), "moe_grouped_simt")
 
 
 def expert_gemm_tc_supported(x: torch.Tensor, hidden: int, inner: int) -> bool:
@@ -559,14 +566,16 @@ def gather_rows(x, out, sorted_pair, top_k: int) -> None:
 
 
 def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
-                   n_experts: int, tile_rows: int, status, gather_top_k: int = 0, weight_experts: int = 0) -> None:
+                   n_experts: int, tile_rows: int, status, gather_top_k: int = 0, weight_experts: int = 0,
+                   act: tuple = (0, 0.0, 1.0)) -> None:
     """Expert products on tcgen05/TMEM fed by TMA.  ``x_rows`` bf16 [pairs, K] in expert order; mode 1:
     ``out[p, :I] = silu(gate) * up`` (bf16), mode 2: ``out[pair(p)] = w[pair(p)] * down`` (float32), mode 3:
     ``out[p] = relu(up)^2`` (bf16; ungated experts, weights ``[E, I, K]``).  The plan's
     tile list must have been made with ``bm = tile_rows``.  Mode 1 or 3 with ``gather_top_k`` > 0: ``x_rows`` is the
     step's activations [T, K] and the kernel fetches the row of token ``pair // gather_top_k`` itself, one
     TMA box a row (for steps of few tokens: it saves the gathered copy and its launch).  ``weight_experts`` > 0: the
-    plan counts ``n_experts`` experts of which only the first so many have weights (and tiles)."""
+    plan counts ``n_experts`` experts of which only the first so many have weights (and tiles).  ``act`` and a
+    ``pair_w`` of None in mode 2 as in ``moe_grouped_simt``."""
     n_x, K = x_rows.shape
     n_pairs = sorted_pair.numel()
     N = out.shape[1]
@@ -580,7 +589,8 @@ def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, t
     _want(out, torch.float32 if mode == 2 else torch.bfloat16, "out")
     _check(lib().qb_expert_gemm_tc(mode, _p(x_rows), _p(weights), _p(out), _p(sorted_pair), _p(pair_w), _p(plan),
                                    _p(tile_expert), _p(tile_row0), tile_expert.numel(), n_pairs, n_experts, K, N,
-                                   int(tile_rows), int(gather_top_k), n_x, _p(status), int(weight_experts), _stream()),
+                                   int(tile_rows), int(gather_top_k), n_x, _p(status), int(weight_experts), int(act[0]),
+                                   ctypes.c_float(act[1]), ctypes.c_float(act[2]), _stream()),
            "expert_gemm_tc")
 
 
@@ -653,11 +663,12 @@ def apply_penalties(logits, prev, prev_off, pparams) -> None:
 
 
 # ---- short convolution, delta-rule recurrence, latent attention ---------------------------------------
-def short_conv(x, weight, state, out, tok_req, req_start, req_slot, *, bias=None, silu: bool = False) -> None:
+def short_conv(x, weight, state, out, tok_req, req_start, req_slot, *, bias=None, silu: bool = False,
+               plain: bool = False) -> None:
     """``out[t] = x[t] + sum_j weight[:, j] * x[t - taps + 1 + j]`` over each request's own rows, the rows
     before a portion taken from ``state`` ``[slots, taps - 1, C]`` (float32, newest last), which then holds
     the request's last ``taps - 1`` inputs.  ``x`` float32 ``[T, C]`` (a column range of wider rows is fine),
-    ``weight`` float32 ``[C, taps]``.  ``silu``: ``out[t] = silu(bias + sum_j ...)`` instead, the input not added back."""
+    ``weight`` float32 ``[C, taps]``.  ``silu``: ``out[t] = silu(bias + sum_j ...)`` instead, the input not added back; ``plain``: the sum alone."""
     _want(x, torch.float32, "x"); _want(weight, torch.float32, "weight"); _want(state, torch.float32, "state")
     T, C = x.shape
     taps = weight.shape[1]
@@ -669,10 +680,12 @@ def short_conv(x, weight, state, out, tok_req, req_start, req_slot, *, bias=None
         _want(bias, torch.float32, "bias")
         if bias.numel() != C or not silu:
             raise ValueError("short_conv: the bias has C numbers and belongs to the silu form")
+    if silu and plain:
+        raise ValueError("short_conv: silu or the sum alone, not both")
     R = req_slot.numel()
     _check(lib().qb_short_conv(ctypes.c_void_p(x.data_ptr()), _p(weight), _p(state), _p(out), _code(out), _p(tok_req),
-                               _p(req_start), _p(req_slot), T, R, C, taps, int(x.stride(0)), _p(bias), int(silu),
-                               _stream()), "short_conv", 2 if taps > 1 else 1)
+                               _p(req_start), _p(req_slot), T, R, C, taps, int(x.stride(0)), _p(bias),
+                               2 if plain else int(silu), _stream()), "short_conv", 2 if taps > 1 else 1)
 
 
 DELTA_RULE_MAX_DIM = 256
@@ -943,3 +956,116 @@ def selective_scan(u, proj, z, dt_pre, dt_bias, A, D, state, out, req_start, req
                                    ctypes.c_void_p(z.data_ptr()), int(z.stride(0)), _p(dt_pre), _p(dt_bias), _p(A), _p(D),
                                    _p(state), _p(out), _p(req_start), _p(req_slot), T, req_slot.numel(), inner,
                                    int(n_state), int(rank), _stream()), "selective_scan")
+
+
+# ---- grouped norms with branch norms and the depth-weighted stream; caps and gated activations ------------------
+NORM_MAX_GROUPS = 64
+
+
+def grouped_normed_add(h, *, y=None, y_scale: float = 1.0, y_bias=None, y_gain=None, extra=None, extra_scale: float = 1.0,
+                       extra_bias=None, extra_gain=None, branch_eps: float = 0.0, gain=None, groups: int = 1,
+                       gain_eps: float = 0.0, history=None, n_history: int = 0, history_weights=None, weight=None,
+                       weight_groups: int = 1, eps: float = 0.0, out=None, rows=None, store_h: bool = True) -> None:
+    """One launch for what lies between two sublayers (all float32; ``h`` ``[T, H]`` is the residual stream):
+
+    ``a = sum_s y[:, s] + y_bias``, ``b = extra + extra_bias``; each is divided by its root mean square over the row
+    (``branch_eps`` inside the root) and multiplied by its gain when ``y_gain`` / ``extra_gain`` is given;
+    ``z = y_scale * a + extra_scale * b``; ``d = gain * z / rms_g(z)`` where the row is cut into ``groups`` equal
+    parts that are each divided by their own root mean square (``gain`` None: ``d = z``); ``x = h + d``.  With
+    ``history`` (float32 ``[entries, T, H]``): entry ``n_history`` receives ``x`` and ``x`` becomes
+    ``sum_{j <= n_history} history_weights[j] * history[j]``.  ``h`` is stored unless ``store_h`` is False;
+    ``out`` (any activation dtype) receives ``weight * x / rms_g(x)`` (``weight_groups`` parts), or ``x`` itself when
+    ``weight`` is None.  ``rows`` (int32) selects token rows for ``out`` (not with ``history``)."""
+    _want(h, torch.float32, "h")
+    T, H = h.shape
+    S = 1
+    if y is not None:
+        _want(y, torch.float32, "y")
+        S = y.shape[1] if y.dim() == 3 else 1
+        if y.shape[0] != T or y.shape[-1] != H:
+            raise ValueError("grouped_normed_add: y shape mismatch")
+    elif extra is not None or gain is not None:
+        raise ValueError("grouped_normed_add: a second addend or a gain without a first addend")
+    for t, n, size in ((y_bias, "y_bias", H), (y_gain, "y_gain", H), (extra, "extra", T * H), (extra_bias, "extra_bias", H),
+                       (extra_gain, "extra_gain", H), (gain, "gain", H), (weight, "weight", H)):
+        if t is not None:
+            _want(t, torch.float32, n)
+            if t.numel() != size:
+                raise ValueError(f"grouped_normed_add: {n} holds {t.numel()} numbers, {size} wanted")
+    for g in (groups, weight_groups):
+        if not 1 <= int(g) <= NORM_MAX_GROUPS or H % int(g):
+            raise ValueError(f"grouped_normed_add: {g} groups do not divide a width of {H} (1 to {NORM_MAX_GROUPS})")
+    hist_stride = 0
+    if history is not None:
+        _want(history, torch.float32, "history"); _want(history_weights, torch.float32, "history_weights")
+        if history.dim() != 3 or tuple(history.shape[1:]) != (T, H) or not 0 <= n_history < history.shape[0] \
+                or history_weights.numel() != n_history + 1 or rows is not None:
+            raise ValueError("grouped_normed_add: history shape mismatch")
+        hist_stride = T * H
+    n = T if rows is None else rows.numel()
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    if out is not None and (out.shape[0] != n or out.shape[1] != H):
+        raise ValueError("grouped_normed_add: out shape mismatch")
+    _check(lib().qb_grouped_normed_add(
+        _p(h), _p(y), S, ctypes.c_float(y_scale), _p(y_bias), _p(y_gain), _p(extra), ctypes.c_float(extra_scale),
+        _p(extra_bias), _p(extra_gain), ctypes.c_float(branch_eps), _p(gain), int(groups), ctypes.c_float(gain_eps),
+        _p(history), ctypes.c_longlong(hist_stride), int(n_history), _p(history_weights),
+        _p(weight) if out is not None else ctypes.c_void_p(0), int(weight_groups), ctypes.c_float(eps), _p(out),
+        _code(out) if out is not None else F32, _p(rows), n, H, int(store_h), _stream()), "grouped_normed_add")
+
+
+def tanh_cap(x: torch.Tensor, cap: float) -> None:
+    """``x <- cap * tanh(x / cap)`` in place (float32)."""
+    _want(x, torch.float32, "x")
+    _check(lib().qb_tanh_cap(_p(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream()), "tanh_cap")
+
+
+GLU_SILU, GLU_CLAMPED = 0, 1
+
+
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, *, bias=None, kind: int = GLU_SILU, limit: float = 0.0,
+            alpha: float = 1.0) -> None:
+    """The activation of a gated dense feed-forward from ``gate_up`` ``[n, 2 I]`` = ``[gate | up]`` (the activation
+    dtype, or the product's float32 accumulators) into ``out`` ``[n, I]``; ``bias`` float32 ``[2 I]`` is added first.
+    ``GLU_SILU``: ``silu(gate) * up``; ``GLU_CLAMPED``: ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``,
+    ``g * sigmoid(alpha * g) * (u + 1)``."""
+    n, two_i = gate_up.shape
+    if tuple(out.shape) != (n, two_i // 2) or (gate_up.dtype != out.dtype and gate_up.dtype != torch.float32):
+        raise ValueError("glu_act: shape/dtype mismatch")
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+        if bias.numel() != two_i:
+            raise ValueError("glu_act: the bias has 2 I numbers")
+    if kind == GLU_CLAMPED and not limit > 0:
+        raise ValueError("glu_act: the clamped form needs a positive limit")
+    _check(lib().qb_glu_act(_p(gate_up), _code(gate_up), _p(bias), _p(out), _code(out), n, two_i // 2, int(kind),
+                            ctypes.c_float(limit), ctypes.c_float(alpha), _stream()), "glu_act")
+
+
+GATED_DELTA_MAX_DIM = 256
+
+
+def gated_delta(qkv, ab, a_off: int, b_off: int, A_log, dt_bias, state, out, req_start, req_slot, n_heads: int,
+                n_groups: int, dim: int, vdim: int, q_scale: float, unit_eps: float) -> None:
+    """The recurrence ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` per (request, head) over the
+    step's tokens, from and into ``state`` ``[slots, heads, dim, vdim]`` float32.  ``qkv`` float32 ``[T, P]`` holds
+    ``q | k`` (groups x dim each; head h reads group ``h // (heads / groups)``) and ``v`` (heads x vdim) in its
+    first columns, after convolution and activation; q and k are made unit vectors per group here (``unit_eps``
+    under the root), q also times ``q_scale``.  ``ab`` float32 rows whose columns ``a_off + h`` / ``b_off + h`` are
+    the pre-activations of the decay ``g = exp(-exp(A_log) * softplus(a + dt_bias))`` and of ``beta = sigmoid(b)``.
+    ``out`` float32 ``[T, heads, vdim]``."""
+    for t, n in ((qkv, "qkv"), (ab, "ab"), (A_log, "A_log"), (dt_bias, "dt_bias"), (state, "state"), (out, "out")):
+        _want(t, torch.float32, n)
+    T = qkv.shape[0]
+    H, G, D, DV = int(n_heads), int(n_groups), int(dim), int(vdim)
+    if (qkv.stride(1) != 1 or ab.stride(1) != 1 or qkv.shape[1] < 2 * G * D + H * DV or ab.shape[0] != T
+            or min(a_off, b_off) < 0 or max(a_off, b_off) + H > ab.shape[1] or out.numel() != T * H * DV
+            or A_log.numel() != H or dt_bias.numel() != H or tuple(state.shape[1:]) != (H, D, DV) or H % G):
+        raise ValueError("gated_delta: shape mismatch")
+    R = req_slot.numel()
+    scratch = torch.empty(T * (2 * G * D + 2 * H), dtype=torch.float32, device=qkv.device)
+    _check(lib().qb_gated_delta(ctypes.c_void_p(qkv.data_ptr()), int(qkv.stride(0)), ctypes.c_void_p(ab.data_ptr()),
+                                int(ab.stride(0)), int(a_off), int(b_off), _p(A_log), _p(dt_bias), _p(state), _p(out),
+                                _p(scratch), _p(req_start), _p(req_slot), R, T, H, G, D, DV, ctypes.c_float(q_scale),
+                                ctypes.c_float(unit_eps), _stream()), "gated_delta", 2)

@@ -1,2 +1,2 @@
 """Architectures: each module maps a configuration to a model specification and registers itself."""
-from . import guravik, minimax_m3, tarulix, tirizen  # noqa: F401
+from . import guravik, minimax_m3, puvolix, tarulix, tirizen  # noqa: F401

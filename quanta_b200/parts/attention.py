@@ -11,7 +11,12 @@ Options beside that formula, all off by default: values of another head size tha
 (``value_dim``); a query temperature ``q *= 1 + coef * ln(floor((p + 1) / every) + 1)`` at position p
 (``q_temperature``); a gate per head, ``out_h *= sigmoid(W_g x)_h`` before the output projection (tensor
 ``names["g"]``, ``[heads, hidden]``, part of the fused input projection); a layer without keys and values
-of its own (``own_kv`` False: no k/v tensors; the model's run order names the entry whose cache it reads).
+of its own (``own_kv`` False: no k/v tensors; the model's run order names the entry whose cache it reads); a short
+causal convolution over time on every channel of the projected q, k and v, before norm and rotation (``conv_taps``
+> 0; tensors ``names["q_conv"]`` / ``k_conv`` / ``v_conv`` ``[channels, taps]``, no bias; the last ``taps - 1``
+projected rows of a request are per-request state, so a portion that starts anywhere sees what the whole prompt
+sees); a learned number per q head that multiplies the head's scores (tensor ``names["head_temperature"]``
+``[heads]``, float32; folded into the normed, rotated query).
 """
 
 from __future__ import annotations
@@ -32,7 +37,7 @@ class GQAttention(Mixer):
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                  position, qk_norm: str | None, qk_norm_eps: float, names: dict, window: int | None = None,
                  value_dim: int | None = None, q_temperature: tuple | None = None, own_kv: bool = True,
-                 float32_output: bool = False):
+                 float32_output: bool = False, conv_taps: int = 0, conv_state_name: str = "attention_conv_inputs"):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} q heads are not a multiple of {n_kv_heads} kv heads")
         value_dim = head_dim if value_dim is None else int(value_dim)
@@ -50,6 +55,11 @@ class GQAttention(Mixer):
         self.position = make("position", position) if isinstance(position, tuple) else position
         self.names = dict(names)      # q, o; k, v with own_kv; q_norm (k_norm) when normed; g for a gate per head
         self.gated = "g" in self.names
+        self.taps, self.conv_state_name = int(conv_taps), conv_state_name
+        if self.taps < 0 or (self.taps and (not self.own_kv or self.gated)):
+            raise ValueError("gqa_attention: the convolution on q, k, v needs keys and values of the layer's own and "
+                             "no gate per head")
+        self.conv_w = self.head_temp = None
         # the tensor-core kernels take equal key and value head sizes that are multiples of 16
         self.mma_shapes = self.hd == self.vd and self.hd % 16 == 0
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
@@ -71,6 +81,12 @@ class GQAttention(Mixer):
             specs.append(TensorSpec(n["q_norm"], (self.nq * hd if self.qk_norm == "per_layer" else hd,), "f32", "gain"))
             if self.own_kv:
                 specs.append(TensorSpec(n["k_norm"], (self.nkv * hd if self.qk_norm == "per_layer" else hd,), "f32", "gain"))
+        if self.taps:
+            specs += [TensorSpec(n["q_conv"], (self.nq * hd, self.taps), "f32", "conv"),
+                      TensorSpec(n["k_conv"], (self.nkv * hd, self.taps), "f32", "conv"),
+                      TensorSpec(n["v_conv"], (self.nkv * vd, self.taps), "f32", "conv")]
+        if "head_temperature" in n:
+            specs.append(TensorSpec(n["head_temperature"], (self.nq,), "f32", "gain"))
         return specs
 
     def load(self, fetch):
@@ -95,6 +111,19 @@ class GQAttention(Mixer):
         if self.qk_norm is not None:
             self.q_norm_w = fetch(n["q_norm"])
             self.k_norm_w = fetch(n["k_norm"]) if self.own_kv else None
+        if self.taps:
+            self.conv_w = torch.cat([fetch(n["q_conv"]), fetch(n["k_conv"]), fetch(n["v_conv"])], 0).contiguous()
+        if "head_temperature" in n:
+            self.head_temp = fetch(n["head_temperature"]).contiguous()
+
+    @property
+    def conv_channels(self) -> int:
+        return self.nq * self.hd + self.nkv * (self.hd + self.vd)
+
+    def state_spec(self):
+        if self.taps > 1:
+            return {self.conv_state_name: ((self.taps - 1, self.conv_channels), torch.float32)}
+        return {}
 
     def cache_spec(self):
         if not self.own_kv:
@@ -104,7 +133,16 @@ class GQAttention(Mixer):
 
     def forward(self, x, ctx, cache, state):
         T = x.shape[0]
-        qkv = linear(x, self.w_qkv)
+        if self.taps:
+            # the projection's float32 accumulators pass the convolution and reach norm and rotation unrounded
+            proj = linear(x, self.w_qkv, out_dtype=torch.float32)
+            C = self.conv_channels
+            qkv = torch.empty((T, C), dtype=torch.float32, device=x.device)
+            hist = state[self.conv_state_name] if self.taps > 1 else \
+                torch.empty((0, 0, C), dtype=torch.float32, device=x.device)
+            kernels.short_conv(proj[:, :C], self.conv_w, hist, qkv, ctx.tok_req, ctx.req_start, ctx.req_slot, plain=True)
+        else:
+            qkv = linear(x, self.w_qkv)
         q = torch.empty((T, self.nq, self.hd), dtype=x.dtype, device=x.device)
         tables = self.position.rotary_tables(x.device)
         if tables is None:
@@ -125,7 +163,8 @@ class GQAttention(Mixer):
             qkv, q, cache.k if cache.write else None, cache.v if cache.write else None, self.q_norm_w,
             self.k_norm_w, _NORM_KIND[self.qk_norm], self.eps, inv_freq, pair_axis, ctx.positions, ctx.tok_pos,
             ctx.tok_req, cache.block_table, self.nq, self.nkv, self.hd, rd, cache.page_size, ctx.status,
-            vd=self.vd, has_kv=self.own_kv, q_temp_coef=self.q_temp[0], q_temp_every=self.q_temp[1])
+            vd=self.vd, has_kv=self.own_kv, q_temp_coef=self.q_temp[0], q_temp_every=self.q_temp[1],
+            head_scale=self.head_temp)
         out = empty_rows(T, self.nq, self.vd, dtype=x.dtype, device=x.device)
         self.attend(q, cache, out, ctx)
         if self.gated:

@@ -58,7 +58,7 @@ class TensorSpec:
     held in float32 whatever the compute dtype (norm gains, router gate and bias: a tensor stored in
     32-bit stays so); ``"i32"`` integer tables.  ``init`` tells the random-weights mode how to draw
     it: ``"normal"`` N(0, 0.02), ``"gain"`` 1 + U(-0.1, 0.1), ``"bias"`` U(-0.05, 0.05), ``"mixing"`` a square matrix, the
-    identity + U(-0.1, 0.1), ``"fraction"`` U(0.2, 0.8).
+    identity + U(-0.1, 0.1), ``"fraction"`` U(0.2, 0.8), ``"depth_mix"`` a vector U(-0.3, 0.3) whose last entry has 1 added, ``"conv"`` taps U(-0.4, 0.4) with 1 added to the newest.
     """
     name: str
     shape: tuple[int, ...]
@@ -211,25 +211,39 @@ class Part:
 
 class Addends:
     """A sublayer's output as a sum that nobody has taken yet:
-    ``scale * (sum_s y[:, s] + bias) + extra_scale * (extra + extra_bias)`` with ``y`` float32 ``[T, H]`` or
-    ``[T, S, H]``, ``extra`` float32 ``[T, H]`` or None and biases of ``H`` numbers or None.  A mixer or feed-forward
-    whose block norms its output may return one instead of a tensor: the norm kernel that reads the output takes
-    the sum in the same launch (an output bias, two branches with a weight each, routed slots and a shared expert)."""
+    ``scale * n_y(sum_s y[:, s] + bias) + extra_scale * n_e(extra + extra_bias)`` with ``y`` float32 ``[T, H]`` or
+    ``[T, S, H]``, ``extra`` float32 ``[T, H]`` or None and biases of ``H`` numbers or None.  ``n_y`` / ``n_e`` are the
+    identity, or with ``y_gain`` / ``extra_gain`` (float32 ``[H]``) an RMS norm of the addend over the whole row with
+    that gain (``branch_eps`` inside the root): two branches that are each normed before they are summed.  A mixer or
+    feed-forward whose block norms its output may return one instead of a tensor: the norm kernel that reads the
+    output takes the sum in the same launch (an output bias, two branches with a weight each, routed slots and a
+    shared expert)."""
 
-    def __init__(self, y, scale: float = 1.0, bias=None, extra=None, extra_scale: float = 1.0, extra_bias=None):
+    def __init__(self, y, scale: float = 1.0, bias=None, extra=None, extra_scale: float = 1.0, extra_bias=None,
+                 y_gain=None, extra_gain=None, branch_eps: float = 0.0):
         self.y, self.scale, self.bias = y, float(scale), bias
         self.extra, self.extra_scale, self.extra_bias = extra, float(extra_scale), extra_bias
+        self.y_gain, self.extra_gain, self.branch_eps = y_gain, extra_gain, float(branch_eps)
+
+    @property
+    def branch_normed(self) -> bool:
+        return self.y_gain is not None or self.extra_gain is not None
 
     def total(self) -> torch.Tensor:
         """The sum as a float32 ``[T, H]`` tensor (plain torch; for tools, not for the step)."""
+        def normed(z, gain):
+            if gain is None:
+                return z
+            return gain * z * torch.rsqrt((z * z).mean(-1, keepdim=True) + self.branch_eps)
+
         y = self.y.float()
         z = y.sum(1) if y.dim() == 3 else y.clone()
         if self.bias is not None:
             z += self.bias
-        z *= self.scale
+        z = normed(z, self.y_gain) * self.scale
         if self.extra is not None:
             e = self.extra.float() + (self.extra_bias if self.extra_bias is not None else 0.0)
-            z += self.extra_scale * e
+            z += self.extra_scale * normed(e, self.extra_gain)
         return z
 
 
@@ -249,7 +263,7 @@ class NormedPending:
     @property
     def y(self) -> torch.Tensor:
         a = self.addends
-        plain = a.y.dim() == 2 and a.scale == 1.0 and a.bias is None and a.extra is None
+        plain = a.y.dim() == 2 and a.scale == 1.0 and a.bias is None and a.extra is None and not a.branch_normed
         return a.y if plain else a.total()
 
     def materialize(self) -> torch.Tensor:

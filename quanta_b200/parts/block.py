@@ -11,7 +11,8 @@ import torch
 
 from .. import kernels
 from ..matmul import empty_rows, linear
-from .base import Block, Embedding, Head, NormedPending, StreamsPending, TensorSpec, make, register
+from . import norms as _norms
+from .base import Addends, Block, Embedding, Head, NormedPending, StreamsPending, TensorSpec, make, register
 
 
 @register("block", "pre_norm")
@@ -163,6 +164,74 @@ class HyperConnectedBlock(Block):
         return StreamsPending(self.feed_forward.forward(u2, ctx), w["mix2"], w["out2"], self.mult)
 
 
+@register("block", "depth_weighted")
+class DepthWeightedBlock(Block):
+    """Any single-stream block, after which the residual stream is replaced by a learned weighted sum of the results
+    so far: with ``X_0`` the stream the first such layer starts from and ``X_(i+1)`` the result of layer ``i`` (the
+    inner block's whole effect on the stream it was given), the stream that goes on is
+    ``sum_{j <= i+1} weights[j] * X_j``.  ``index`` is ``i``; ``weights_name`` names a float32 tensor of ``i + 2``
+    numbers.  The results of the step's tokens are kept in one float32 tensor ``[depth + 1, T, hidden]`` that the
+    layers of a step share (``ctx.work``); the inner block's last contribution joins the stream, the result is
+    stored and the weighted sum is taken in ONE launch."""
+
+    def __init__(self, hidden_size: int, inner, index: int, depth: int, weights_name: str, history_key: str = "depth_results"):
+        if not 0 <= int(index) < int(depth):
+            raise ValueError(f"depth_weighted: layer {index} of {depth}")
+        self.hidden, self.index, self.depth = int(hidden_size), int(index), int(depth)
+        self.inner = make("block", inner)
+        self.weights_name, self.history_key = weights_name, history_key
+        self.weights = None
+        self.graph_safe = bool(getattr(self.inner, "graph_safe", False))
+
+    # the model asks a block for its mixer and feed-forward (cache needs, routing traces)
+    @property
+    def mixer(self):
+        return self.inner.mixer
+
+    @property
+    def feed_forward(self):
+        return getattr(self.inner, "feed_forward", None)
+
+    def children(self):
+        return [self.inner]
+
+    def state_spec(self):
+        return self.inner.state_spec()
+
+    def tensor_specs(self):
+        return [TensorSpec(self.weights_name, (self.index + 2,), "f32", "depth_mix")]
+
+    def load(self, fetch):
+        self.weights = fetch(self.weights_name).contiguous()
+
+    def forward(self, h, pending, ctx, cache, state):
+        if h.dim() != 2:
+            raise NotImplementedError("a depth-weighted stream is built for one residual stream")
+        if pending is not None:
+            raise ValueError("a depth-weighted layer starts from a finished stream (nothing pending)")
+        T = h.shape[0]
+        hist = ctx.work.get(self.history_key)
+        if self.index == 0 or hist is None:
+            if self.index != 0:
+                raise ValueError("depth_weighted: the results of the earlier layers of this step are missing")
+            hist = ctx.work[self.history_key] = torch.empty((self.depth + 1, T, self.hidden), dtype=torch.float32,
+                                                            device=h.device)
+            hist[0].copy_(h)
+        d = self.inner.forward(h, None, ctx, cache, state)
+        if isinstance(d, NormedPending) and isinstance(d.norm, _norms.RMSNorm):
+            _norms.normed_add(h, d, None, 0.0, None, None, True, history=hist, n_history=self.index + 1,
+                              history_weights=self.weights)
+            return None
+        if isinstance(d, (NormedPending, Addends)):
+            d = d.materialize() if isinstance(d, NormedPending) else d.total()
+        if isinstance(d, StreamsPending):
+            raise NotImplementedError("a depth-weighted stream is built for one residual stream")
+        if d is not None and d.dtype != torch.float32:
+            d = d.float()
+        kernels.grouped_normed_add(h, y=d, history=hist, n_history=self.index + 1, history_weights=self.weights)
+        return None
+
+
 @register("embedding", "token_table")
 class TokenTable(Embedding):
     """``h = table[ids] * scale`` into the float32 residual stream (src/quanta/minimax/model.py:91; the
@@ -205,13 +274,17 @@ class TokenTable(Embedding):
 class LinearHead(Head):
     """Final norm on the wanted rows, then ``logits = x @ head.T`` in float32
     (src/quanta/minimax/runtime.py:95-98).  ``tied_to`` names the embedding table to reuse (a tensor that
-    two parts ask for by the same name is loaded once and shared); ``logit_scale`` multiplies the logits."""
+    two parts ask for by the same name is loaded once and shared); ``logit_scale`` multiplies the logits;
+    ``softcap`` > 0: ``logits <- softcap * tanh(logits / softcap)`` at the end."""
 
     graph_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int, norm, weight_name: str | None, tied_to: str | None,
-                 logit_scale: float = 1.0):
+                 logit_scale: float = 1.0, softcap: float = 0.0):
         self.V, self.H, self.logit_scale = int(vocab_size), int(hidden_size), float(logit_scale)
+        self.softcap = float(softcap)
+        if self.softcap < 0:
+            raise ValueError(f"linear head: a cap of {softcap} on the logits")
         self.norm = make("norm", norm)
         self.weight_name, self.tied_to = weight_name, tied_to
         self.weight = None
@@ -232,4 +305,8 @@ class LinearHead(Head):
         logits = linear(x, self.weight, out_dtype=torch.float32)
         if self.logit_scale != 1.0:
             logits.mul_(self.logit_scale)       # on the float32 products: one rounding, as the formula has it
+        if self.softcap > 0.0:
+            if not logits.is_contiguous():
+                logits = logits.contiguous()
+            kernels.tanh_cap(logits, self.softcap)
         return logits

@@ -29,6 +29,9 @@ class SigmoidTopKExperts(FeedForward):
 
     # the first product of an expert: 1 = silu(gate x) * (up x) from [gate; up] rows, 3 = relu(up x)^2
     first_product_mode = 1
+    # (kind, limit, alpha) of a gated first product, see kernels.moe_grouped_simt; with the clamped kind the routing
+    # weight multiplies the expert's input (inside the first product) and the down product takes no weights
+    expert_act = (kernels.EXPERT_ACT_SILU, 0.0, 1.0)
 
     @property
     def graph_safe(self):
@@ -163,24 +166,26 @@ class SigmoidTopKExperts(FeedForward):
             self.trace.append(idx)
         act = torch.empty((n_pairs, self.I), dtype=x.dtype, device=dev)
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)
+        ea = self.expert_act
+        w_down = None if ea[0] == kernels.EXPERT_ACT_CLAMPED else w.view(-1)
         if path == "tc":
             # bfloat16: TMA-fed tcgen05 products, weights as the 128-row operand, accumulators in TMEM
             if n_pairs <= self.gather_in_kernel_max_rows * self.E:
                 # few tokens: the kernel fetches each pair's token row itself
                 kernels.expert_gemm_tc(self.first_product_mode, x, self.w13, act, sorted_pair, w.view(-1), plan,
                                        tile_expert, tile_row0, self.E, bm, ctx.status, gather_top_k=self.k,
-                                       weight_experts=self.E_w)
+                                       weight_experts=self.E_w, act=ea)
             else:
                 xg = torch.empty((n_pairs, self.H), dtype=x.dtype, device=dev)
                 kernels.gather_rows(x, xg, sorted_pair, self.k)
                 kernels.expert_gemm_tc(self.first_product_mode, xg, self.w13, act, sorted_pair, w.view(-1), plan,
-                                       tile_expert, tile_row0, self.E, bm, ctx.status, weight_experts=self.E_w)
-            kernels.expert_gemm_tc(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
+                                       tile_expert, tile_row0, self.E, bm, ctx.status, weight_experts=self.E_w, act=ea)
+            kernels.expert_gemm_tc(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w_down, plan,
                                    tile_expert, tile_row0, self.E, bm, ctx.status, weight_experts=self.E_w)
         else:
-            kernels.moe_grouped_simt(self.first_product_mode, x, self.w13, act, sorted_pair, w, plan, tile_expert,
-                                     tile_row0, self.E, self.k)
-            kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
+            kernels.moe_grouped_simt(self.first_product_mode, x, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert,
+                                     tile_row0, self.E, self.k, act=ea)
+            kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w_down, plan,
                                      tile_expert, tile_row0, self.E, self.k)
         if self.E_w < self.E:
             # the chosen experts past the last one with weights hand the token through, times its weight
@@ -287,3 +292,41 @@ class SoftmaxSharedExperts(SigmoidTopKExperts):
         if self.shared is None:
             return Addends(y)
         return Addends(y, extra=self.shared.forward(x, ctx))
+
+
+@register("feed_forward", "input_weighted_experts")
+class InputWeightedExperts(SigmoidTopKExperts):
+    """Sigmoid-routed gated experts whose routing weight multiplies the expert's INPUT: the output is the sum over
+    the chosen experts of ``expert(w * x)``.  Router logits float32, scores ``sigmoid``, the ``top_k`` largest chosen
+    (the lower index among equals), the weights the chosen scores as they are.  An expert has no biases:
+    ``g = min(W_gate z, limit)``, ``u = clamp(W_up z, -limit, limit)``, ``W_down (g * sigmoid(alpha g) * (u + 1))``.
+    Both first products are linear in their input, so the weight is applied to their float32 accumulators.
+    ``shared_size`` > 0: an expert of the same form (its own ``shared_limit``) that every token passes with weight
+    one is added.  ``names``: gate (the router), templates w1 / w3 / w2 with ``{e}`` (an expert's gate, up, down) and
+    shared_gate / shared_up / shared_down.  Returns the routed slots with the shared expert's output as a second
+    addend, for a block that norms the sum."""
+
+    def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top_k: int, limit: float, alpha: float,
+                 names: dict, shared_size: int = 0, shared_limit: float = 0.0):
+        super().__init__(hidden_size, expert_size, n_experts, top_k, use_bias=False, renormalize=False, scaling=1.0,
+                         names=names)
+        if not limit > 0:
+            raise ValueError(f"input_weighted_experts: a clamp at {limit}")
+        self.expert_act = (kernels.EXPERT_ACT_CLAMPED, float(limit), float(alpha))
+        self.shared_size = int(shared_size)
+        self.shared = None
+        if self.shared_size:
+            from .dense import GatedDense
+            self.shared = GatedDense(hidden_size, shared_size, {"gate": names["shared_gate"], "up": names["shared_up"],
+                                                                "down": names["shared_down"]},
+                                     activation="clamped", limit=float(shared_limit), alpha=float(alpha))
+
+    def children(self):
+        return [self.shared] if self.shared is not None else []
+
+    def forward(self, x, ctx):
+        y = super().forward(x, ctx)
+        if self.shared is None:
+            return Addends(y)
+        extra = self.shared.forward(x, ctx)
+        return Addends(y, extra=extra.y if isinstance(extra, Addends) else extra)

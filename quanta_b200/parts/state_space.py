@@ -11,9 +11,11 @@ inputs are per-request state.  Step sizes, decays, the state and the gate are fl
 library products whose float32 accumulators feed the kernels (the step projection multiplies the float32 ``low``
 with the float32 copy of ``W_dt``; its bias and softplus are applied inside the scan).
 
-``parallel_mixers``: two mixers read the same input; the result is ``left_scale * left + right_scale * right``.
-Their caches and states live side by side (stream and state names must differ); the sum is left to the norm
-kernel that reads the mixer's output when the block has one.
+``parallel_mixers``: two mixers read the same input; the result is ``left_scale * left + right_scale * right``,
+or with ``left_norm`` / ``right_norm`` ``left_scale * norm_l(left) + right_scale * norm_r(right)`` (each branch
+RMS-normed over the whole width with a gain of its own first).  Their caches and states live side by side (stream
+and state names must differ); the sum, and the branch norms, are left to the norm kernel that reads the mixer's
+output when the block has one.
 """
 
 from __future__ import annotations
@@ -83,13 +85,21 @@ class SelectiveScan(Mixer):
 class ParallelMixers(Mixer):
     graph_safe = True
 
-    def __init__(self, left, right, left_scale: float = 1.0, right_scale: float = 1.0):
+    def __init__(self, left, right, left_scale: float = 1.0, right_scale: float = 1.0, left_norm=None,
+                 right_norm=None):
         self.left, self.right = make("mixer", left), make("mixer", right)
         self.left_scale, self.right_scale = float(left_scale), float(right_scale)
+        self.left_norm = make("norm", left_norm) if left_norm is not None else None
+        self.right_norm = make("norm", right_norm) if right_norm is not None else None
+        for n in (self.left_norm, self.right_norm):
+            if n is not None and (not hasattr(n, "weight") or getattr(n, "groups", 1) != 1):
+                raise ValueError("parallel_mixers: a branch norm is an rms_norm over the whole width")
+        if self.left_norm is not None and self.right_norm is not None and self.left_norm.eps != self.right_norm.eps:
+            raise ValueError("parallel_mixers: the two branch norms share one eps")
         self.graph_safe = bool(getattr(self.left, "graph_safe", False) and getattr(self.right, "graph_safe", False))
 
     def children(self):
-        return [self.left, self.right]
+        return [p for p in (self.left, self.right, self.left_norm, self.right_norm) if p is not None]
 
     def cache_spec(self):
         specs = []
@@ -112,9 +122,11 @@ class ParallelMixers(Mixer):
         b = self.right.forward(x, ctx, cache, state)
         a = a if isinstance(a, Addends) else Addends(a)
         b = b if isinstance(b, Addends) else Addends(b)
-        if a.extra is not None or a.y.dim() != 2:
+        if a.extra is not None or a.y.dim() != 2 or a.branch_normed or (self.left_norm is not None and a.scale != 1.0):
             a = Addends(a.total())
-        if b.extra is not None or b.y.dim() != 2 or b.scale != 1.0:
+        if b.extra is not None or b.y.dim() != 2 or b.scale != 1.0 or b.branch_normed:
             b = Addends(b.total())
+        eps = (self.left_norm or self.right_norm).eps if (self.left_norm or self.right_norm) is not None else 0.0
         return Addends(a.y, scale=a.scale * self.left_scale, bias=a.bias, extra=b.y, extra_scale=self.right_scale,
-                       extra_bias=b.bias)
+                       extra_bias=b.bias, y_gain=None if self.left_norm is None else self.left_norm.weight,
+                       extra_gain=None if self.right_norm is None else self.right_norm.weight, branch_eps=eps)

@@ -110,6 +110,14 @@ class RandomSource:
             # a square matrix near the identity: what mixes residual streams must not blow them up
             t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(-0.1, 0.1, generator=g)
             t += torch.eye(s.shape[0], dtype=torch.float32, device=device)
+        elif s.init == "conv":
+            # taps of a short convolution: the newest near one, the older ones a fraction of it
+            t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(-0.4, 0.4, generator=g)
+            t[..., -1] += 1.0
+        elif s.init == "depth_mix":
+            # weights of a sum over the results of the layers so far: the newest near one, the others small
+            t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(-0.3, 0.3, generator=g)
+            t[-1] += 1.0
         elif s.init == "fraction":
             t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(0.2, 0.8, generator=g)
         else:
