@@ -372,7 +372,7 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
       // weights: every row counts once
       for (int i = threadIdx.x - 64; i < NT; i += EPI_THREADS) {
         const int pr = i < rows ? sorted_pair[row0 + i] : 0;
-        s_pair[i] = pr;
+        if (MODE == 2) s_pair[i] = pr;      // in the first product s_pair holds the token rows the producer fetches
         s_w[i] = i < rows ? (pair_w != nullptr ? pair_w[pr] : 1.f) : 0.f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");      // the epilogue warps

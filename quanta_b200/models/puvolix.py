@@ -42,7 +42,7 @@ def softmax_branch(cfg: PuvolixConfig, i: int, m: dict) -> tuple[str, dict]:
     return ("gqa_attention", dict(
         hidden_size=cfg.width, n_q_heads=int(m["heads"]), n_kv_heads=int(m["kv_heads"]), head_dim=int(m["dim"]),
         value_dim=int(m["vdim"]), scale=float(m["scale"]), position=position, qk_norm="per_head",
-        qk_norm_eps=cfg.norm_eps, names=names, float32_output=True, conv_taps=taps))
+        qk_norm_eps=cfg.norm_eps, names=names, float32_output=True, conv_taps=taps, float32_weights=True))
 
 
 def delta_branch(cfg: PuvolixConfig, i: int, m: dict) -> tuple[str, dict]:

@@ -16,7 +16,9 @@ causal convolution over time on every channel of the projected q, k and v, befor
 > 0; tensors ``names["q_conv"]`` / ``k_conv`` / ``v_conv`` ``[channels, taps]``, no bias; the last ``taps - 1``
 projected rows of a request are per-request state, so a portion that starts anywhere sees what the whole prompt
 sees); a learned number per q head that multiplies the head's scores (tensor ``names["head_temperature"]``
-``[heads]``, float32; folded into the normed, rotated query).
+``[heads]``, float32; folded into the normed, rotated query); softmax weights that stay 32-bit on the tensor
+cores too (``float32_weights``: the kernels that feed ``P V`` with the weights in two bfloat16 parts, and float32
+arithmetic for single tokens, instead of the kernels that round the weights to bfloat16).
 """
 
 from __future__ import annotations
@@ -37,7 +39,8 @@ class GQAttention(Mixer):
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                  position, qk_norm: str | None, qk_norm_eps: float, names: dict, window: int | None = None,
                  value_dim: int | None = None, q_temperature: tuple | None = None, own_kv: bool = True,
-                 float32_output: bool = False, conv_taps: int = 0, conv_state_name: str = "attention_conv_inputs"):
+                 float32_output: bool = False, conv_taps: int = 0, conv_state_name: str = "attention_conv_inputs",
+                 float32_weights: bool = False):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} q heads are not a multiple of {n_kv_heads} kv heads")
         value_dim = head_dim if value_dim is None else int(value_dim)
@@ -60,12 +63,13 @@ class GQAttention(Mixer):
             raise ValueError("gqa_attention: the convolution on q, k, v needs keys and values of the layer's own and "
                              "no gate per head")
         self.conv_w = self.head_temp = None
+        self.float32_weights = bool(float32_weights)
         # the tensor-core kernels take equal key and value head sizes that are multiples of 16
         self.mma_shapes = self.hd == self.vd and self.hd % 16 == 0
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
         # more q heads per kv head than the single-token kernel takes: single tokens run as portions of one,
         # whose tile list comes from the host each step, so such a model's decode steps are not captured
-        self.graph_safe = self.nq // self.nkv <= kernels.ATTN_DECODE_MAX_GROUP
+        self.graph_safe = self.float32_weights or self.nq // self.nkv <= kernels.ATTN_DECODE_MAX_GROUP
 
     def children(self):
         return [self.position]
@@ -178,6 +182,15 @@ class GQAttention(Mixer):
         tokens (the keys of all of them dealt evenly over the SMs) and one for portions (tiles of
         token-by-head rows)."""
         window = self.window or 0
+        if self.float32_weights:
+            # scores and weights in float32 whatever the dtype: portions of shapes the tensor cores take run there
+            # with the weights in two bfloat16 parts; single tokens cut their keys into ranges that are joined
+            R = int(ctx.req_start.numel()) - 1
+            warps = max(1, q.shape[0] * self.nkv)
+            n_split = max(1, min(-(-8192 // warps), -(-max(1, ctx.max_len_after) // 32), 64))
+            kernels.window_attention(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.block_table, self.scale,
+                                     window, ctx.status, n_split=n_split, n_requests=R)
+            return
         if q.dtype != torch.bfloat16 or not self.mma_shapes:
             kernels.paged_attention_simt(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.block_table,
                                          self.scale, window, ctx.status)

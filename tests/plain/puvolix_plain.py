@@ -99,14 +99,24 @@ def softmax_attention(w, p: str, h, m: dict, eps: float):
     if dims:
         f = scaled_frequencies(dims, float(rot["base"]), rot.get("scaling"), h.dtype)
         q, k = rotate(q, pos, dims, f), rotate(k, pos, dims, f)
-    out = h.new_zeros(T, H, V)
+    out = attend(q, k, v, float(m["scale"]), w[p + "temp"])
+    return out.reshape(T, H * V) @ w[p + "o"].T
+
+
+def attend(q, k, v, scale: float, temp):
+    """Causal softmax attention of one sequence: ``q`` [T, H, D], ``k`` [T, G, D], ``v`` [T, G, V], a number per head
+    (``temp`` [H]) on the scaled scores -> [T, H, V]."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    pos = torch.arange(T, device=q.device)
     mask = pos[None, :] <= pos[:, None]
+    out = q.new_zeros(T, H, v.shape[2])
     for head in range(H):
         g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * float(m["scale"]) * w[p + "temp"][head]
+        s = (q[:, head] @ k[:, g].T) * scale * temp[head]
         s = s.masked_fill(~mask, float("-inf"))
         out[:, head] = torch.softmax(s, -1) @ v[:, g]
-    return out.reshape(T, H * V) @ w[p + "o"].T
+    return out
 
 
 def gated_delta_rule(w, p: str, h, m: dict, eps: float):
@@ -121,8 +131,19 @@ def gated_delta_rule(w, p: str, h, m: dict, eps: float):
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(h @ w[p + "b"].T)                                                   # [T, H]
     decay = torch.exp(-torch.exp(w[p + "A_log"]) * F.softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))
-    S = h.new_zeros(H, D, V)
-    o = h.new_zeros(T, H, V)
+    o, _ = delta_recurrence(q, k, v, decay, beta)
+    o = rms(o, eps) * w[p + "norm"]
+    o = o * F.silu(h @ w[p + "g"].T).view(T, H, V)
+    return o.reshape(T, H * V) @ w[p + "o"].T
+
+
+def delta_recurrence(q, k, v, decay, beta, S=None):
+    """``q``, ``k`` [T, G, D]; ``v`` [T, H, V]; ``decay``, ``beta`` [T, H].  Per head, in this order:
+    ``S <- decay S``; ``u = beta (v - S^T k)``; ``S <- S + k u^T``; ``o = S^T q``.  Returns (o [T, H, V], S)."""
+    T, H, V = v.shape
+    G, D = k.shape[1], k.shape[2]
+    S = v.new_zeros(H, D, V) if S is None else S.clone()
+    o = v.new_zeros(T, H, V)
     for t in range(T):
         for head in range(H):
             g = head // (H // G)
@@ -130,9 +151,7 @@ def gated_delta_rule(w, p: str, h, m: dict, eps: float):
             u = beta[t, head] * (v[t, head] - S[head].T @ k[t, g])
             S[head] = S[head] + torch.outer(k[t, g], u)
             o[t, head] = S[head].T @ q[t, g]
-    o = rms(o, eps) * w[p + "norm"]
-    o = o * F.silu(h @ w[p + "g"].T).view(T, H, V)
-    return o.reshape(T, H * V) @ w[p + "o"].T
+    return o, S
 
 
 def parallel_mixer(w, p: str, h, m: dict, eps: float):
@@ -154,15 +173,22 @@ def clamped_expert(w, p: str, h, limit: float):
 
 
 def router_choice(w, p: str, h, top: int):
-    """(experts [T, top], their sigmoid scores [T, top]); equal scores go to the lower index."""
+    """(experts [T, top], their sigmoid scores [T, top], margin [T]); equal scores go to the lower index.  The
+    margin is the gap between the last chosen score and the best one left out (a choice rounding could turn)."""
     s = torch.sigmoid(h.float() @ w[p + "router"].float().T)
-    order = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :top]
-    return order, torch.gather(s, 1, order)
+    ranked = torch.sort(s, dim=-1, descending=True, stable=True)
+    order = ranked.indices[:, :top]
+    margin = ranked.values[:, top - 1] - ranked.values[:, top] if s.shape[1] > top else torch.full((h.shape[0],), 1e9)
+    return order, torch.gather(s, 1, order), margin
 
 
-def routed_ff(w, p: str, h, mlp: dict):
+def routed_ff(w, p: str, h, mlp: dict, chosen=None):
+    """``chosen`` [T, top]: take these experts (with their own scores) instead of the router's choice."""
     top, limit = int(mlp["router"]["top"]), float(mlp["expert"]["limit"])
-    idx, score = router_choice(w, p, h, top)
+    idx, score, margin = router_choice(w, p, h, top)
+    if chosen is not None:
+        idx = chosen.to(idx.device).long()
+        score = torch.gather(torch.sigmoid(h.float() @ w[p + "router"].float().T), 1, idx)
     y = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for c in range(top):
@@ -171,39 +197,126 @@ def routed_ff(w, p: str, h, mlp: dict):
     shared = mlp.get("shared")
     if shared is not None:
         y = y + clamped_expert(w, p + "shared.", h, float(shared["limit"]))
-    return y
+    return y, idx, margin
 
 
-def feed_forward(w, p: str, h, mlp: dict):
-    return dense_ff(w, p, h) if mlp.get("kind") == "dense" else routed_ff(w, p, h, mlp)
-
-
-def forward(weights: dict, config: dict, tokens, dtype=torch.float32, with_layers: bool = False,
-            before_average: bool = False):
-    """Logits ``[T, vocab]`` of one whole sequence; with ``with_layers`` also the stream after every layer
-    (``before_average``: each layer's own result instead of what goes on to the next)."""
+def forward(weights: dict, config: dict, tokens, dtype=torch.float32, chosen=None, details: bool = False):
+    """Logits ``[T, vocab]`` of one whole sequence.  ``chosen``: one ``[T, top]`` tensor per routed layer, in layer
+    order, that replaces the router's choice.  ``details``: also a dictionary with ``layers`` (the stream that goes
+    on after every layer), ``results`` (every layer's own result, before the weighted sum) and ``routing`` (per
+    routed layer the chosen experts and the margin of the choice)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
-    eps, groups = float(config["norm"]["eps"]), int(config["norm"].get("groups", 1))
+    eps, groups = float(config["norm"]["eps"]), int(config["norm"].get("groups") or 1)
     ids = torch.as_tensor(tokens, dtype=torch.long, device=w["embed"].device)
     x = w["embed"][ids]
-    results = [x]
-    trace = []
+    results, after, routing = [x], [], []
+    chosen = list(chosen) if chosen is not None else None
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
         if layer["type"] != "parallel":
             raise ValueError(f"layer type {layer['type']!r}")
         x = x + grouped_norm(parallel_mixer(w, p + "mix.", x, layer["mixer"], eps), w[p + "norm1"], groups, eps)
-        if layer.get("mlp") is not None:
-            x = x + grouped_norm(feed_forward(w, p + "mlp.", x, layer["mlp"]), w[p + "norm2"], groups, eps)
+        mlp = layer.get("mlp")
+        if mlp is not None and mlp.get("kind") == "dense":
+            x = x + grouped_norm(dense_ff(w, p + "mlp.", x), w[p + "norm2"], groups, eps)
+        elif mlp is not None:
+            y, idx, margin = routed_ff(w, p + "mlp.", x, mlp, chosen.pop(0) if chosen is not None else None)
+            routing.append((idx, margin))
+            x = x + grouped_norm(y, w[p + "norm2"], groups, eps)
         results.append(x)
-        if before_average:
-            trace.append(x)
         x = sum(w[p + "dwa"][j] * results[j] for j in range(i + 2))
-        if not before_average:
-            trace.append(x)
+        after.append(x)
     x = grouped_norm(x, w["final.norm"], groups, eps)
     logits = x @ w["head"].T
     cap = float(config.get("logit_softcap") or 0.0)
     if cap:
         logits = cap * torch.tanh(logits / cap)
-    return (logits, torch.stack(trace)) if with_layers else logits
+    if details:
+        return logits, {"layers": torch.stack(after), "results": torch.stack(results[1:]), "routing": routing}
+    return logits
+
+
+def generate(weights: dict, config: dict, prompt, n_new: int) -> list[int]:
+    """Greedy continuation, the whole sequence run again for every token."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(forward(weights, config, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+# ---- random weights of a configuration ----------------------------------------------------------------------
+def tensor_shapes(config: dict) -> dict:
+    W, V = int(config["width"]), int(config["vocab"])
+    shapes = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+    for i, layer in enumerate(config["layers"]):
+        p = f"l{i}."
+        shapes[p + "norm1"] = (W,)
+        shapes[p + "dwa"] = (i + 2,)
+        l, r = layer["mixer"]["left"], layer["mixer"]["right"]
+        H, G, D, Vd = int(l["heads"]), int(l["kv_heads"]), int(l["dim"]), int(l["vdim"])
+        q = p + "mix.left."
+        shapes.update({q + "q": (H * D, W), q + "k": (G * D, W), q + "v": (G * Vd, W), q + "o": (W, H * Vd),
+                       q + "q.norm": (D,), q + "k.norm": (D,), q + "temp": (H,), q + "out": (W,)})
+        taps = int(l.get("conv") or 0)
+        if taps:
+            shapes.update({q + "q.conv": (H * D, taps), q + "k.conv": (G * D, taps), q + "v.conv": (G * Vd, taps)})
+        H, G, D, Vd = int(r["heads"]), int(r["kv_heads"]), int(r["dim"]), int(r["vdim"])
+        q = p + "mix.right."
+        shapes.update({q + "q": (G * D, W), q + "k": (G * D, W), q + "v": (H * Vd, W), q + "g": (H * Vd, W),
+                       q + "b": (H, W), q + "a": (H, W), q + "A_log": (H,), q + "dt_bias": (H,), q + "norm": (Vd,),
+                       q + "o": (W, H * Vd), q + "out": (W,)})
+        taps = int(r.get("conv") or 0)
+        if taps:
+            shapes.update({q + "q.conv": (G * D, taps), q + "k.conv": (G * D, taps), q + "v.conv": (H * Vd, taps)})
+        mlp = layer.get("mlp")
+        if mlp is None:
+            continue
+        shapes[p + "norm2"] = (W,)
+        q = p + "mlp."
+        if mlp["kind"] == "dense":
+            F_ = int(mlp["ff"])
+            shapes.update({q + "gate": (F_, W), q + "gate.b": (F_,), q + "up": (F_, W), q + "up.b": (F_,),
+                           q + "down": (W, F_), q + "down.b": (W,)})
+        else:
+            F_ = int(mlp["expert"]["ff"])
+            shapes[q + "router"] = (int(mlp["router"]["experts"]), W)
+            for e in range(int(mlp["router"]["experts"])):
+                shapes.update({f"{q}e{e}.gate": (F_, W), f"{q}e{e}.up": (F_, W), f"{q}e{e}.down": (W, F_)})
+            if mlp.get("shared") is not None:
+                S = int(mlp["shared"]["ff"])
+                shapes.update({q + "shared.gate": (S, W), q + "shared.up": (S, W), q + "shared.down": (W, S)})
+    return shapes
+
+
+def draw_weights(config: dict, seed: int) -> dict:
+    """bfloat16 tensors by name, drawn so that no constant of the design is near neutral: gains away from one,
+    taps of every age, weights of the depth sum of both signs, decays between slow and fast."""
+    g = torch.Generator().manual_seed(seed)
+    uni = lambda shape, lo, hi: torch.empty(shape).uniform_(lo, hi, generator=g)  # noqa: E731
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if name.endswith(".conv"):
+            t = uni(shape, -0.5, 0.5)
+            t[:, -1] += 1.0
+        elif leaf in ("norm1", "norm2", "norm", "out") or name == "final.norm":
+            t = uni(shape, 0.6, 1.4)
+        elif leaf == "temp":
+            t = uni(shape, 0.5, 2.0)
+        elif leaf == "dwa":
+            t = uni(shape, -0.4, 0.4)
+            t[-1] += 1.0
+        elif leaf == "A_log":
+            t = uni(shape, -2.0, 1.0)
+        elif leaf == "dt_bias":
+            t = uni(shape, -1.0, 1.0)
+        elif leaf == "b" and len(shape) == 1:
+            t = uni(shape, -0.3, 0.3)
+        elif leaf == "router":
+            t = torch.randn(shape, generator=g) * 2.0 / math.sqrt(shape[1])
+        elif name == "embed":
+            t = torch.randn(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) * 1.5 / math.sqrt(shape[-1])
+        out[name] = t.to(torch.bfloat16)
+    return out
