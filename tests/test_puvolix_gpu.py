@@ -61,7 +61,7 @@ CONFIGS = {
     "B": _config(130, 96, [
         _layer(_left(3, 1, 24, 40, 5, (24, 30.0, (8.0, 0.5, 2.0, 64))), _right(6, 2, 16, 12, 1), None),
         _layer(_left(8, 4, 12, 12, 3, (4, 1e4, None)), _right(2, 2, 40, 24, 4), _moe(4, 3, 32, 0.7, (8, 3.0))),
-        _layer(_left(2, 1, 36, 6, 2, (36, 250.0, (2.0, 1.0, 8.0, 16))), _right(4, 1, 8, 20, 3), _dense(72)),
+        _layer(_left(2, 1, 36, 6, 2, (36, 250.0, (2.0, 1.0, 8.0, 16))), _right(4, 1, 24, 20, 3), _dense(72)),
         _layer(_left(4, 4, 16, 16, 3, (16, 77.0, None)), _right(1, 1, 32, 32, 2), _moe(2, 2, 48, 1.0))], eps=1e-6, groups=1),
     "C": _config(61, 44, [
         _layer(_left(2, 1, 22, 10, 3, (10, 9.0, (4.0, 1.0, 4.0, 30))), _right(2, 1, 18, 26, 2), _moe(9, 1, 8, 1.5, (12, 1.0))),
@@ -242,7 +242,7 @@ ORDERS = {
     "routed_only": [_layer(_left(2, 1, 16, 16, 3, (16, 1e3, (4.0, 1.0, 4.0, 32))), _right(2, 2, 16, 16, 4), _FF),
                     _layer(_left(2, 1, 16, 16, 3, (16, 1e3, (4.0, 1.0, 4.0, 32))), _right(2, 2, 16, 16, 4), _moe(6, 3, 8, 0.5))],
     "dense_between": [_layer(_left(4, 2, 8, 12, 4, (4, 20.0, None)), _right(2, 1, 12, 8, 2), _FF),
-                      _layer(_left(2, 1, 20, 8, 2, (20, 2e4, (16.0, 1.0, 2.0, 24))), _right(4, 4, 8, 8, 3), _dense(40)),
+                      _layer(_left(2, 1, 20, 8, 2, (20, 2e4, (16.0, 1.0, 2.0, 24))), _right(4, 4, 16, 8, 3), _dense(40)),
                       _layer(_left(1, 1, 24, 24, 3), _right(1, 1, 24, 24, 4), None),
                       _layer(_left(4, 2, 8, 12, 4, (4, 20.0, None)), _right(2, 1, 12, 8, 2), _FF)],
 }

@@ -152,7 +152,7 @@ def test_short_convolution_across_portions(taps, silu):
 def test_rescaled_frequencies():
     """The ladder after rescaling by wavelength, in all three ranges, against the plain function."""
     from quanta_b200.parts.rotary import PartialRotary
-    for dims, base, sc in [(40, 130000.0, (6.0, 1.0, 4.0, 1024)), (16, 100.0, (8.0, 0.5, 2.0, 64)), (8, 9.0, (3.0, 1.0, 3.0, 40)),
+    for dims, base, sc in [(40, 130000.0, (6.0, 1.0, 4.0, 1024)), (16, 100.0, (8.0, 0.5, 2.0, 64)), (8, 900.0, (3.0, 1.0, 3.0, 40)),
                            (32, 1e4, None)]:
         part = PartialRotary(head_dim=dims + 8, rotary_dim=dims, theta=base, wavelength_scaling=sc)
         scaling = None if sc is None else dict(zip(("factor", "low", "high", "original"), sc))
