@@ -5,6 +5,7 @@
     python bench.py --design guravik      (another workload: see bench_designs.py; the default one is unchanged)
     python bench.py --design tirizen      (likewise)
     python bench.py --design tarulix      (likewise)
+    python bench.py --design puvolix      (likewise; also beside Tarulix, the closest model)
 
 One JSON line on standard output.  A "step" is one decode step of the whole batch.  The default run
 has the layer sizes of the baseline's third configuration (hidden 3072, 48 q / 8 kv heads of 128,
@@ -313,7 +314,7 @@ def main() -> int:
                     help="feed the prompts of the decode runs in portions of this many tokens (0: whole)")
     ap.add_argument("--no-e2e", dest="e2e", action="store_false", help="skip the run through the Python entry point")
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
-    ap.add_argument("--design", default=None, choices=["guravik", "tirizen", "tarulix"],
+    ap.add_argument("--design", default=None, choices=["guravik", "tirizen", "tarulix", "puvolix"],
                     help="instead of the default workload: prefill and decode throughput of this design beside the "
                          "MiniMax-M3 decoder at equal sizes, and its kernels alone against their bounds (bench_designs.py)")
     ap.add_argument("--sizes", default="", help="with --design: the sizes to run, comma separated (default: all)")

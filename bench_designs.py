@@ -1,4 +1,4 @@
-"""``bench.py --design guravik`` / ``--design tirizen`` / ``--design tarulix``: another decoder beside the MiniMax-M3 decoder at equal sizes.
+"""``bench.py --design guravik`` / ``--design tirizen`` / ``--design tarulix`` / ``--design puvolix``: another decoder beside the MiniMax-M3 decoder at equal sizes.
 
 For a few sizes that resemble a real model's layers (seeded random weights, bfloat16): one prompt of
 ``--prompt-len`` tokens as one step (tokens a second) and decode steps of ``--batch`` requests at that
@@ -26,6 +26,14 @@ distance bias, sink and blended values, then a rotary windowed attention with po
 routed, pass-through and shared experts).  Alone: ``window_attention`` in both forms over a prompt (flops / time /
 tensor peak) and over single tokens deep in a context (visible cache bytes / time / copy bandwidth) beside the
 softmax-attention kernels of MiniMax-M3, and ``selective_scan`` beside Tirizen's gated linear recurrence.
+
+``--design puvolix``: the Puvolix decoder (every layer a softmax attention with 32-bit weights beside a gated delta
+rule; a dense layer with biases first, then routed experts with a shared expert; norms in groups; a depth-weighted
+stream) beside Tarulix, the closest existing model (a parallel attention and recurrence, output norms, routed and
+shared experts), and MiniMax-M3, all at equal sizes.  Alone: the attention kernels in the form Puvolix runs them
+(no window) beside Tarulix's biased form and MiniMax-M3's; ``gated_delta`` beside Guravik's ``delta_rule`` (the like
+chain in time) and Tirizen's ``gla``; the launch between two sublayers (``grouped_normed_add`` with branch norms,
+and with the depth-weighted sum) beside ``normed_add_rmsnorm``.
 """
 
 from __future__ import annotations
@@ -86,6 +94,31 @@ TARULIX_SIZES = {
     "w4096": dict(width=4096, groups=2, vocab=32000, ff=11008, attn_heads=32, dim=128, window=1024, pool=64, rot=64, inner=8192,
                   state=16, dt_rank=256, taps=4),
 }
+
+
+PUVOLIX_SIZES = {
+    "w2048": dict(width=2048, groups=2, vocab=32000, ff=5632, attn_heads=16, dim=128, rot=64, delta_heads=16, delta_groups=8,
+                  delta_dim=128, norm_groups=8, window=1024, pool=64, inner=4096, state=16, dt_rank=128, taps=4),
+    "w4096": dict(width=4096, groups=2, vocab=32000, ff=11008, attn_heads=32, dim=128, rot=64, delta_heads=32, delta_groups=16,
+                  delta_dim=128, norm_groups=8, window=1024, pool=64, inner=8192, state=16, dt_rank=256, taps=4),
+}
+
+
+def puvolix_raw(s: dict) -> dict:
+    """Six layers, each a softmax attention (a quarter as many kv heads, half the head rotated, rescaled frequencies,
+    convolutions of 4 taps) beside a gated delta rule (heads of 128 x 128 in groups of two, convolutions of 4 taps);
+    the first layer's feed-forward dense with biases, the others 8 routed experts of which 2 are chosen and a shared
+    expert, together as wide as ``ff``."""
+    moe = {"kind": "moe", "expert": {"ff": 3 * s["ff"] // 8, "limit": 7.0}, "router": {"experts": 8, "top": 2},
+           "shared": {"ff": s["ff"] // 4, "limit": 7.0}}
+    left = {"heads": s["attn_heads"], "kv_heads": max(1, s["attn_heads"] // 4), "dim": s["dim"], "vdim": s["dim"], "conv": 4,
+            "scale": 1.0 / math.sqrt(s["dim"]),
+            "rot": {"dims": s["rot"], "base": 5e5, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": s["delta_heads"], "kv_heads": s["delta_groups"], "dim": s["delta_dim"], "vdim": s["delta_dim"], "conv": 4}
+    layers = [{"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)},
+               "mlp": {"kind": "dense", "ff": s["ff"]} if i == 0 else moe} for i in range(3 * s["groups"])]
+    return {"architecture": "Puvolix", "vocab": s["vocab"], "width": s["width"], "layers": layers,
+            "norm": {"eps": 1e-5, "groups": s["norm_groups"]}, "logit_softcap": 30.0}
 
 
 def tarulix_raw(s: dict) -> dict:
@@ -384,6 +417,158 @@ def window_attn(tokens_per_req: int, reqs: int, context: int, nq: int, nkv: int,
             "TFLOP/s": round(flops / ms / 1e9, 2), "GB/s": round(nbytes / ms / 1e6, 1)}
 
 
+def plain_attn(tokens_per_req: int, reqs: int, context: int, nq: int, nkv: int, hd: int, page: int = 16) -> dict:
+    """The attention as Puvolix runs it: ``window_attention`` over all keys, no extras; portions on the tensor cores
+    with the weights in two bfloat16 parts, single tokens with their keys cut into ranges and a join (32-bit
+    arithmetic).  Flops count ``4 * head_dim`` a (query head, visible key); bytes the visible keys and values once."""
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    per = -(-context // page)
+    single = tokens_per_req == 1
+    layers = 1 if not single else max(1, min(16, int(3e9 // (2 * reqs * per * nkv * page * hd * 2))))
+    caches = [(torch.randn(reqs * per, nkv, page, hd, device=dev, dtype=torch.bfloat16),
+               torch.randn(reqs * per, nkv, page, hd, device=dev, dtype=torch.bfloat16)) for _ in range(layers)]
+    table = torch.randperm(reqs * per, dtype=torch.int32).view(reqs, per).to(dev)
+    T = tokens_per_req * reqs
+    q = torch.randn(T, nq, hd, device=dev, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.arange(context - tokens_per_req, context, dtype=torch.int32, device=dev).repeat(reqs)
+    req = torch.arange(reqs, dtype=torch.int32, device=dev).repeat_interleave(tokens_per_req)
+    st = k.new_status(dev)
+    n_split = max(1, min(-(-8192 // (T * nkv)), -(-context // 32), 64))       # as parts/attention.py chooses it
+
+    def all_layers():
+        for kc, vc in caches:
+            k.window_attention(q, kc, vc, out, pos, req, table, hd ** -0.5, 0, st, n_split=n_split, n_requests=reqs)
+    ms = (bk.timed_graph(all_layers, reps=1) if single else bk.timed(all_layers, n=5, warm=2)) / layers
+    k.raise_on_status(st.cpu())
+    seen = sum(p_ + 1 for p_ in range(context - tokens_per_req, context))
+    flops = 4.0 * hd * nq * seen * reqs
+    nbytes = reqs * context * nkv * hd * 2 * 2
+    return {"kernel": "window_attention (all keys, no extras)", "requests": reqs, "tokens_per_request": tokens_per_req,
+            "context": context, "q_heads": nq, "kv_heads": nkv, "head_dim": hd, "layers": layers, "ranges": n_split if single else 1,
+            "us": round(ms * 1e3, 2), "TFLOP/s": round(flops / ms / 1e9, 2), "GB/s": round(nbytes / ms / 1e6, 1)}
+
+
+def gated_delta(tokens_per_req: int, reqs: int, heads: int, groups: int, D: int, DV: int) -> dict:
+    """``gated_delta`` alone (preparation + chain).  Bytes: the state read and written, and per token the rows read
+    (q, k, v, the two pre-activations), the unit q and k written and read, and the output."""
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    T = tokens_per_req * reqs
+    C = 2 * groups * D + heads * DV
+    qkv = torch.randn(T, C, device=dev)
+    ab = torch.randn(T, 2 * heads, device=dev)
+    A_log, dt_b = torch.zeros(heads, device=dev), torch.zeros(heads, device=dev)
+    layers = 1 if tokens_per_req > 1 else max(1, min(16, int(2e9 // (reqs * heads * D * DV * 4))))
+    states = [torch.zeros(reqs, heads, D, DV, device=dev) for _ in range(layers)]
+    out = torch.empty(T, heads, DV, device=dev)
+    starts = torch.arange(0, T + 1, tokens_per_req, dtype=torch.int32, device=dev)
+    slots = torch.arange(reqs, dtype=torch.int32, device=dev)
+
+    def all_layers():
+        for s in states:
+            k.gated_delta(qkv, ab, 0, heads, A_log, dt_b, s, out, starts, slots, heads, groups, D, DV, D ** -0.5, 1e-6)
+    ms = (bk.timed_graph(all_layers, reps=1) if tokens_per_req == 1 else bk.timed(all_layers, n=5, warm=2)) / layers
+    nbytes = 2 * reqs * heads * D * DV * 4 + T * (C + 2 * heads + 4 * groups * D + heads * DV) * 4
+    return {"kernel": "gated_delta (preparation + chain)", "requests": reqs, "tokens_per_request": tokens_per_req, "heads": heads,
+            "groups": groups, "dim": D, "value_dim": DV, "layers": layers, "us": round(ms * 1e3, 2),
+            "tokens/s": round(T / ms * 1e3, 1), "GB/s": round(nbytes / ms / 1e6, 1),
+            "fp32 TFLOP/s": round(7.0 * D * DV * heads * T / ms / 1e9, 2)}
+
+
+def between_sublayers(tokens: int, H: int, groups: int, depth: int) -> dict:
+    """One launch between two sublayers, bytes / time: ``grouped_normed_add`` with two normed branches and a norm in
+    groups (the mixer's output joins the stream, the feed-forward reads it), the same with routed slots, a shared
+    expert and the depth-weighted sum over ``depth`` earlier results, and ``normed_add_rmsnorm`` (one norm over the
+    row, two addends) for comparison."""
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    h = torch.randn(tokens, H, device=dev)
+    a, b = torch.randn(tokens, H, device=dev), torch.randn(tokens, H, device=dev)
+    slots = torch.randn(tokens, 2, H, device=dev)
+    g1, g2, g = (torch.rand(H, device=dev) + 0.5 for _ in range(3))
+    out = torch.empty(tokens, H, device=dev, dtype=torch.bfloat16)
+    hist = torch.randn(depth + 1, tokens, H, device=dev)
+    w = torch.rand(depth + 1, device=dev)
+    small = tokens <= 64
+    run = (lambda f: bk.timed_graph(f, reps=20)) if small else (lambda f: bk.timed(f, n=10, warm=3))
+    t_mix = run(lambda: k.grouped_normed_add(h, y=a, y_scale=0.5, y_gain=g1, extra=b, extra_scale=0.5, extra_gain=g2, branch_eps=1e-5,
+                                             gain=g, groups=groups, gain_eps=1e-5, out=out))
+    t_depth = run(lambda: k.grouped_normed_add(h, y=slots, extra=b, gain=g, groups=groups, gain_eps=1e-5, history=hist,
+                                               n_history=depth, history_weights=w))
+    t_old = run(lambda: k.normed_add_rmsnorm(h, a, g, 1e-5, None, 0.0, out, y_scale=0.5, extra=b, extra_scale=0.5))
+    row = H * 4
+    by = {"branches + group norm": tokens * (4 * row + H * 2), "slots + shared + depth sum": tokens * ((5 + depth + 1) * row),
+          "normed_add_rmsnorm": tokens * (4 * row + H * 2)}
+    res = {"tokens": tokens, "width": H, "groups": groups, "depth": depth}
+    for name, ms in (("branches + group norm", t_mix), ("slots + shared + depth sum", t_depth), ("normed_add_rmsnorm", t_old)):
+        res[name] = {"us": round(ms * 1e3, 2), "GB/s": round(by[name] / ms / 1e6, 1)}
+    return res
+
+
+def run_puvolix(args) -> dict:
+    import bench
+    import bench_kernels as bk
+    from quanta_b200.config import MiniMaxM3Config, PuvolixConfig, TarulixConfig
+    pk, pk_src = bench.peaks()
+    clocks = bench.ClockSampler()
+    clocks.start()
+    models = {}
+    for name, s in PUVOLIX_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        t0 = time.time()
+        p = _model_numbers(PuvolixConfig.from_dict(puvolix_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        t = _model_numbers(TarulixConfig.from_dict(tarulix_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        m = _model_numbers(MiniMaxM3Config.from_dict(minimax_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        models[name] = {"sizes": s, "puvolix": p, "tarulix": t, "minimax_m3": m}
+        print(f"[bench] {name}: puvolix {p}\n[bench] {name}: tarulix {t}\n[bench] {name}: minimax_m3 {m} ({time.time() - t0:.0f} s)",
+              file=sys.stderr, flush=True)
+    s = PUVOLIX_SIZES["w2048"]
+    T, B = args.prompt_len, args.batch
+    tensor, hbm = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    Hq, Hk, hd = s["attn_heads"], max(1, s["attn_heads"] // 4), s["dim"]
+    pp, pd = plain_attn(T, 1, T, Hq, Hk, hd), plain_attn(1, B, T, Hq, Hk, hd)
+    tp, td = window_attn(T, 1, T, Hq, Hk, hd, s["window"], "biased"), window_attn(1, B, 4 * T, Hq, Hk, hd, s["window"], "biased")
+    sp, sd = bk.attn_span(T, 0, Hq, Hk, hd, 16), bk.attn_decode(B, T, Hq, Hk, hd, 16)
+    for r in (pp, tp, sp):
+        r["frac_of_tensor_peak"] = round(r["TFLOP/s"] * 1e12 / tensor, 4)
+    for r in (pd, td, sd):
+        r["frac_of_copy_bandwidth"] = round(r["GB/s"] * 1e9 / hbm, 4)
+    H_, G_, D_ = s["delta_heads"], s["delta_groups"], s["delta_dim"]
+    gp, gd, gd64 = gated_delta(T, 1, H_, G_, D_, D_), gated_delta(1, B, H_, G_, D_, D_), gated_delta(1, 64, H_, G_, D_, D_)
+    dp, dd = delta_rule(T, 1, H_, D_), delta_rule(1, B, H_, D_)
+    lp, ld = gla(T, 1, H_, D_, D_), gla(1, B, H_, D_, D_)
+    for r in (gp, gd, gd64, dp, dd, lp, ld):
+        r["frac_of_copy_bandwidth"] = round(r["GB/s"] * 1e9 / hbm, 4)
+    bp, bd = between_sublayers(T, s["width"], s["norm_groups"], 6), between_sublayers(B, s["width"], s["norm_groups"], 6)
+    for r in (bp, bd):
+        for v in r.values():
+            if isinstance(v, dict):
+                v["frac_of_copy_bandwidth"] = round(v["GB/s"] * 1e9 / hbm, 4)
+    kernels_alone = {"prompt_attention": {"puvolix": pp, "tarulix": tp, "minimax_m3": sp},
+                     "single_token_attention": {"puvolix": pd, "tarulix": td, "minimax_m3": sd},
+                     "recurrence_prompt": {"puvolix": gp, "guravik_delta_rule": dp, "tirizen_gla": lp},
+                     "recurrence_single_tokens": {"puvolix": gd, "puvolix_batch_64": gd64, "guravik_delta_rule": dd, "tirizen_gla": ld},
+                     "between_sublayers_prompt": bp, "between_sublayers_single_tokens": bd}
+    for k_, v in kernels_alone.items():
+        print(f"[bench] {k_}: {v}", file=sys.stderr, flush=True)
+    first = next(iter(models.values()))["puvolix"] if models else {}
+    return {"metric": f"Puvolix decode tokens/s (batch {args.batch}, {args.prompt_len}-token prompts) beside Tarulix and MiniMax-M3 at equal sizes",
+            "value": first.get("decode_tok_s"), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": first.get("decode_ms"), "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic (seeded uniform token ids, seeded random weights)", "design": "puvolix", "models": models,
+            "kernels": kernels_alone, "peaks": {**pk, "source": pk_src}, "clocks": clocks.stop(),
+            "gpu_launches": first.get("launches_per_decode_step", 0) * args.steps, "impl": "ours"}
+
+
 def scan(tokens_per_req: int, reqs: int, inner: int, N: int, rank: int) -> dict:
     """``selective_scan`` alone (the float32 step projection, a library product, and the chain in time).  Bytes: the state read and written, and per token
     u (bfloat16), z, dt written and read, the output (bfloat16) and the projection row."""
@@ -466,6 +651,8 @@ def run(args) -> dict:
         return run_tirizen(args)
     if getattr(args, "design", "guravik") == "tarulix":
         return run_tarulix(args)
+    if getattr(args, "design", "guravik") == "puvolix":
+        return run_puvolix(args)
     import torch
     import bench
     import bench_kernels as bk

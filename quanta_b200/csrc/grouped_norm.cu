@@ -52,6 +52,21 @@ __device__ __forceinline__ void gn_group_inv(const float* buf, int H, int G, flo
   __syncthreads();
 }
 
+// Two block-wide sums at once, each in the fixed order of qb_block_sum.  `scratch` holds >= 64 floats.
+__device__ __forceinline__ void gn_block_sum2(float& a, float& b, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  a = qb_warp_sum(a);
+  b = qb_warp_sum(b);
+  __syncthreads();
+  if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+  for (int w = 0; w < nwarps; ++w) { ta += scratch[w]; tb += scratch[32 + w]; }
+  a = ta;
+  b = tb;
+}
+
 template <typename O>
 __global__ void grouped_normed_add_kernel(
     float* __restrict__ h, const float* __restrict__ y, int S, float y_scale, const float* __restrict__ y_bias,
@@ -63,8 +78,8 @@ __global__ void grouped_normed_add_kernel(
   extern __shared__ float gn_smem[];
   float* buf = gn_smem;                  // H
   float* buf2 = buf + H;                 // H
-  float* scratch = buf2 + H;             // 32
-  float* psum = scratch + 32;            // GN_MAX_CHUNKS
+  float* scratch = buf2 + H;             // 64
+  float* psum = scratch + 64;            // GN_MAX_CHUNKS
   float* ginv = psum + GN_MAX_CHUNKS;    // GN_MAX_GROUPS
   const int r = blockIdx.x;
   if (r >= n_rows) return;
@@ -74,6 +89,7 @@ __global__ void grouped_normed_add_kernel(
     const float* yrow = y + (size_t)tok * S * H;
     const float* y2row = y2 ? y2 + (size_t)tok * H : nullptr;
     float ss1 = 0.f, ss2 = 0.f;
+#pragma unroll 4
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = yrow[i];
       for (int s = 1; s < S; ++s) v += yrow[(size_t)s * H + i];
@@ -87,15 +103,17 @@ __global__ void grouped_normed_add_kernel(
       }
     }
     float inv1 = 1.f, inv2 = 1.f;
-    if (y_gain) inv1 = rsqrtf(qb_block_sum(ss1, scratch) / (float)H + eps_branch);
-    if (y2row && y2_gain) inv2 = rsqrtf(qb_block_sum(ss2, scratch) / (float)H + eps_branch);
+    if (y_gain != nullptr || (y2row != nullptr && y2_gain != nullptr)) {
+      gn_block_sum2(ss1, ss2, scratch);
+      if (y_gain) inv1 = rsqrtf(ss1 / (float)H + eps_branch);
+      if (y2row && y2_gain) inv2 = rsqrtf(ss2 / (float)H + eps_branch);
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float z = y_scale * (y_gain ? y_gain[i] * (buf[i] * inv1) : buf[i]);
       if (y2row) z += y2_scale * (y2_gain ? y2_gain[i] * (buf2[i] * inv2) : buf2[i]);
       buf[i] = z;
     }
     if (g != nullptr) {
-      __syncthreads();
       gn_group_inv(buf, H, g_groups, eps_y, scratch, psum, ginv);
       const int gw = H / g_groups;
       for (int i = threadIdx.x; i < H; i += blockDim.x) buf[i] = hrow[i] + g[i] * (buf[i] * ginv[i / gw]);
@@ -107,12 +125,25 @@ __global__ void grouped_normed_add_kernel(
   }
   // every thread has touched the same elements of buf in each loop so far: they are its own
   if (hist != nullptr) {
+    // the weights of the sum once into shared memory; the earlier results of an element are asked for eight at a
+    // time before any of them is used (the additions stay in the order j = 0, 1, ...)
+    __syncthreads();
+    for (int j = threadIdx.x; j <= n_hist; j += blockDim.x) psum[j] = dwa[j];
+    __syncthreads();
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       const float x = buf[i];
-      hist[(size_t)n_hist * hist_stride + (size_t)tok * H + i] = x;
+      float* hp = hist + (size_t)tok * H + i;
+      hp[(size_t)n_hist * hist_stride] = x;
       float acc = 0.f;
-      for (int j = 0; j < n_hist; ++j) acc += dwa[j] * hist[(size_t)j * hist_stride + (size_t)tok * H + i];
-      acc += dwa[n_hist] * x;
+      for (int j0 = 0; j0 < n_hist; j0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = j0 + u < n_hist ? hp[(size_t)(j0 + u) * hist_stride] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (j0 + u < n_hist) acc += psum[j0 + u] * v[u];
+      }
+      acc += psum[n_hist] * x;
       buf[i] = acc;
     }
   }
@@ -125,7 +156,6 @@ __global__ void grouped_normed_add_kernel(
     for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = qb_from_float<O>(buf[i]);
     return;
   }
-  __syncthreads();
   gn_group_inv(buf, H, w_groups, eps, scratch, psum, ginv);
   const int gw = H / w_groups;
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = qb_from_float<O>(w[i] * (buf[i] * ginv[i / gw]));
@@ -142,9 +172,9 @@ extern "C" int qb_grouped_normed_add(
     float eps, void* out, int out_dtype, const int* rows, int n_rows, int H, int store_h, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (S < 1 || H <= 0 || (y == nullptr && (y2 != nullptr || g != nullptr))) return QB_ERR_BAD_ARG;
-  if (hist != nullptr && (dwa == nullptr || n_hist < 0 || rows != nullptr)) return QB_ERR_BAD_ARG;
+  if (hist != nullptr && (dwa == nullptr || n_hist < 0 || n_hist >= GN_MAX_CHUNKS || rows != nullptr)) return QB_ERR_BAD_ARG;
   if ((g != nullptr && !gn_groups_ok(H, g_groups)) || (w != nullptr && !gn_groups_ok(H, w_groups))) return QB_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)(2 * H + 32 + GN_MAX_CHUNKS + GN_MAX_GROUPS) * sizeof(float);
+  const size_t smem = (size_t)(2 * H + 64 + GN_MAX_CHUNKS + GN_MAX_GROUPS) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
   const int threads = H >= 2048 ? 512 : 256;
   QB_DISPATCH_DTYPE(out_dtype, O, {

@@ -15,7 +15,7 @@ import torch
 from .. import kernels, matmul
 from ..config.registry import load_config
 from ..parts import block as _block  # noqa: F401  (registers the built-in block, embedding and head)
-from ..parts.base import CacheSpec, Part, StreamsPending, TensorSpec, make
+from ..parts.base import CacheSpec, Part, StreamCopy, StreamsPending, TensorSpec, make
 from ..parts.spec import ModelSpec
 from ..weights.loader import FolderSource, RandomSource, open_fetch
 from ..weights.safetensors_io import write_safetensors
@@ -32,7 +32,10 @@ def parse_dtype(d) -> torch.dtype:
 
 
 def _plain(pending):
-    """A pending contribution as a tensor (one that is normed first is normed now)."""
+    """A pending contribution as a tensor (one that is normed first is normed now; a copy that came with a finished
+    stream is no contribution)."""
+    if isinstance(pending, StreamCopy):
+        return None
     return pending.materialize() if hasattr(pending, "materialize") else pending
 
 
@@ -46,7 +49,7 @@ def _stream_now(h, pending):
         kernels.streams_mix_rmsnorm(x, y, mix, out_w, mult, None, None, 0.0, out, store=False)
         return out
     now = h.clone()
-    if pending is not None:
+    if _plain(pending) is not None:
         kernels.residual_add(now, _plain(pending))
     return now
 
@@ -132,9 +135,9 @@ class Model:
                 if h.dim() == 3:
                     raise NotImplementedError("adding the embedding again is not built for several residual streams")
                 # the stream so far, then the embedded tokens once more, both summed in float32
-                if pending is not None:
+                if _plain(pending) is not None:
                     kernels.residual_add(h, _plain(pending))
-                    pending = None
+                pending = None
                 kernels.residual_add(h, embedded)
             pending = self.blocks[entry.layer].forward(h, pending, ctx, caches[pos], states[pos])
             if self.residual_trace is not None:

@@ -685,7 +685,8 @@ def short_conv(x, weight, state, out, tok_req, req_start, req_slot, *, bias=None
     R = req_slot.numel()
     _check(lib().qb_short_conv(ctypes.c_void_p(x.data_ptr()), _p(weight), _p(state), _p(out), _code(out), _p(tok_req),
                                _p(req_start), _p(req_slot), T, R, C, taps, int(x.stride(0)), _p(bias),
-                               2 if plain else int(silu), _stream()), "short_conv", 2 if taps > 1 else 1)
+                               2 if plain else int(silu), _stream()), "short_conv",
+           2 if taps > 1 and not lib().qb_short_conv_one_launch(T, R) else 1)
 
 
 DELTA_RULE_MAX_DIM = 256

@@ -273,6 +273,15 @@ class NormedPending:
         return d
 
 
+class StreamCopy:
+    """Nothing is pending, and the residual stream as it stands is already at hand in the activation dtype (``x``
+    ``[T, H]``, laid out by ``matmul.empty_rows``): whoever finished the stream wrote the copy in the same launch, so
+    a sublayer that reads the stream without a norm needs no launch of its own to get it."""
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+
+
 class StreamsPending:
     """A pending contribution of a model that keeps several residual streams ``x_1 .. x_S``: the sublayer's output
     ``y`` (``[T, H]``, or ``[T, K, H]`` partial results that are added in order) and how it is written back,

@@ -12,7 +12,7 @@ import torch
 from .. import kernels
 from ..matmul import empty_rows, linear
 from . import norms as _norms
-from .base import Addends, Block, Embedding, Head, NormedPending, StreamsPending, TensorSpec, make, register
+from .base import Addends, Block, Embedding, Head, NormedPending, StreamCopy, StreamsPending, TensorSpec, make, register
 
 
 @register("block", "pre_norm")
@@ -77,8 +77,20 @@ class SandwichNormBlock(Block):
 
     def forward(self, h, pending, ctx, cache, state):
         T = h.shape[0]
-        x = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
-        if self.conv is None:
+        if isinstance(pending, StreamCopy):
+            # the stream is finished and its copy in the activation dtype came with it
+            ready, pending = pending.x, None
+            if self.conv is None and isinstance(self.mixer_norm, _norms.NoNorm) and ready.dtype == ctx.dtype:
+                x = ready
+            else:
+                ready = None
+        else:
+            ready = None
+        if ready is None:
+            x = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
+        if ready is not None:
+            pass
+        elif self.conv is None:
             self.mixer_norm.forward(h, pending, x)
         else:
             normed = torch.empty((T, self.hidden), dtype=torch.float32, device=h.device)
@@ -207,6 +219,9 @@ class DepthWeightedBlock(Block):
     def forward(self, h, pending, ctx, cache, state):
         if h.dim() != 2:
             raise NotImplementedError("a depth-weighted stream is built for one residual stream")
+        ready = None
+        if isinstance(pending, StreamCopy):
+            ready, pending = pending, None
         if pending is not None:
             raise ValueError("a depth-weighted layer starts from a finished stream (nothing pending)")
         T = h.shape[0]
@@ -217,19 +232,21 @@ class DepthWeightedBlock(Block):
             hist = ctx.work[self.history_key] = torch.empty((self.depth + 1, T, self.hidden), dtype=torch.float32,
                                                             device=h.device)
             hist[0].copy_(h)
-        d = self.inner.forward(h, None, ctx, cache, state)
+        d = self.inner.forward(h, ready, ctx, cache, state)
+        # the next layer of the stack reads the stream it is given: its copy in the activation dtype is written here
+        out = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device) if self.index + 1 < self.depth else None
         if isinstance(d, NormedPending) and isinstance(d.norm, _norms.RMSNorm):
-            _norms.normed_add(h, d, None, 0.0, None, None, True, history=hist, n_history=self.index + 1,
+            _norms.normed_add(h, d, None, 0.0, out, None, True, history=hist, n_history=self.index + 1,
                               history_weights=self.weights)
-            return None
+            return StreamCopy(out) if out is not None else None
         if isinstance(d, (NormedPending, Addends)):
             d = d.materialize() if isinstance(d, NormedPending) else d.total()
         if isinstance(d, StreamsPending):
             raise NotImplementedError("a depth-weighted stream is built for one residual stream")
         if d is not None and d.dtype != torch.float32:
             d = d.float()
-        kernels.grouped_normed_add(h, y=d, history=hist, n_history=self.index + 1, history_weights=self.weights)
-        return None
+        kernels.grouped_normed_add(h, y=d, history=hist, n_history=self.index + 1, history_weights=self.weights, out=out)
+        return StreamCopy(out) if out is not None else None
 
 
 @register("embedding", "token_table")

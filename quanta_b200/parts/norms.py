@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import Norm, NormedPending, StreamsPending, TensorSpec, register
+from .base import Norm, NormedPending, StreamCopy, StreamsPending, TensorSpec, register
 
 
 @register("norm", "rms_norm")
@@ -46,6 +46,8 @@ class RMSNorm(Norm):
         kernels.streams_mix_rmsnorm(x, y, mix, out_w, mult, read_w, self.weight, self.eps, out, rows=rows, store=store)
 
     def forward(self, h, delta, out, rows=None, store_h=True):
+        if isinstance(delta, StreamCopy):
+            delta = None                # nothing is pending; the copy that came with the stream is not needed here
         if h.dim() == 3 or isinstance(delta, StreamsPending):
             # several residual streams: whoever asks for the plain norm (the output head) reads their sum
             self.forward_streams(h, delta, None, out, rows=rows, store=store_h)
@@ -97,6 +99,8 @@ class NoNorm(Norm):
         self.width = int(width)
 
     def forward(self, h, delta, out, rows=None, store_h=True):
+        if isinstance(delta, StreamCopy):
+            delta = None
         if h.dim() == 3 or isinstance(delta, StreamsPending):
             raise NotImplementedError("reading several residual streams without a norm is not built")
         if isinstance(delta, NormedPending) and isinstance(delta.norm, RMSNorm):
