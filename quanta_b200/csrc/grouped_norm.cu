@@ -20,13 +20,46 @@
 #define GN_CHUNK 256
 #define GN_MAX_CHUNKS 512
 
+// V consecutive floats (V = 4: one 16-byte move from an address that is a multiple of 16 bytes; V = 1: one float)
+template <int V> __device__ __forceinline__ void gn_ld(const float* p, float (&v)[V]) {
+  if constexpr (V == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    v[0] = *p;
+  }
+}
+template <int V> __device__ __forceinline__ void gn_st(float* p, const float (&v)[V]) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else *p = v[0];
+}
+template <typename O, int V> __device__ __forceinline__ void gn_st_out(O* p, const float (&v)[V]) {
+  if constexpr (V == 4 && sizeof(O) == 2) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else if constexpr (V == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+    *p = qb_from_float<O>(v[0]);
+  }
+}
+
 // 1 / sqrt(mean(buf[group]^2) + eps) of every group into ginv.  One group: the block's fixed-order sum.  Several:
 // a warp a chunk of up to GN_CHUNK elements of a group, then a group's chunks added in order.
+template <int V>
 __device__ __forceinline__ void gn_group_inv(const float* buf, int H, int G, float eps, float* scratch, float* psum,
                                              float* ginv) {
   if (G == 1) {
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) ss += buf[i] * buf[i];
+    for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+      float v[V];
+      gn_ld<V>(buf + i, v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) ss += v[e] * v[e];
+    }
     const float total = qb_block_sum(ss, scratch);
     if (threadIdx.x == 0) ginv[0] = rsqrtf(total / (float)H + eps);
     __syncthreads();
@@ -39,7 +72,12 @@ __device__ __forceinline__ void gn_group_inv(const float* buf, int H, int G, flo
   for (int c = warp; c < G * nc; c += nwarps) {
     const int g = c / nc, lo = (c % nc) * GN_CHUNK, hi = min(gw, lo + GN_CHUNK);
     float s = 0.f;
-    for (int i = lo + lane; i < hi; i += 32) { const float v = buf[g * gw + i]; s += v * v; }
+    for (int i = lo + lane * V; i < hi; i += 32 * V) {
+      float v[V];
+      gn_ld<V>(buf + g * gw + i, v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) s += v[e] * v[e];
+    }
     s = qb_warp_sum(s);
     if (lane == 0) psum[c] = s;
   }
@@ -67,7 +105,9 @@ __device__ __forceinline__ void gn_block_sum2(float& a, float& b, float* scratch
   b = tb;
 }
 
-template <typename O>
+// V = 4: the row moves in 16-byte pieces (the width and both group widths are multiples of 4 and every pointer is a
+// multiple of 16 bytes); V = 1: element by element.  A thread touches the same elements of the row in every pass.
+template <typename O, int V>
 __global__ void grouped_normed_add_kernel(
     float* __restrict__ h, const float* __restrict__ y, int S, float y_scale, const float* __restrict__ y_bias,
     const float* __restrict__ y_gain, const float* __restrict__ y2, float y2_scale, const float* __restrict__ y2_bias,
@@ -75,7 +115,7 @@ __global__ void grouped_normed_add_kernel(
     float* __restrict__ hist, size_t hist_stride, int n_hist, const float* __restrict__ dwa,
     const float* __restrict__ w, int w_groups, float eps, O* __restrict__ out, const int* __restrict__ rows,
     int n_rows, int H, int store_h) {
-  extern __shared__ float gn_smem[];
+  extern __shared__ __align__(16) float gn_smem[];
   float* buf = gn_smem;                  // H
   float* buf2 = buf + H;                 // H
   float* scratch = buf2 + H;             // 64
@@ -85,21 +125,38 @@ __global__ void grouped_normed_add_kernel(
   if (r >= n_rows) return;
   const int tok = rows ? rows[r] : r;
   float* hrow = h + (size_t)tok * H;
+  const int i0 = threadIdx.x * V, di = blockDim.x * V;
   if (y != nullptr) {
     const float* yrow = y + (size_t)tok * S * H;
     const float* y2row = y2 ? y2 + (size_t)tok * H : nullptr;
     float ss1 = 0.f, ss2 = 0.f;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      float v = yrow[i];
-      for (int s = 1; s < S; ++s) v += yrow[(size_t)s * H + i];
-      if (y_bias) v += y_bias[i];
-      buf[i] = v;
-      ss1 += v * v;
+#pragma unroll 2
+    for (int i = i0; i < H; i += di) {
+      float v[V], t[V];
+      gn_ld<V>(yrow + i, v);
+      for (int s = 1; s < S; ++s) {
+        gn_ld<V>(yrow + (size_t)s * H + i, t);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] += t[e];
+      }
+      if (y_bias) {
+        gn_ld<V>(y_bias + i, t);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] += t[e];
+      }
+      gn_st<V>(buf + i, v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) ss1 += v[e] * v[e];
       if (y2row) {
-        const float v2 = y2row[i] + (y2_bias ? y2_bias[i] : 0.f);
-        buf2[i] = v2;
-        ss2 += v2 * v2;
+        gn_ld<V>(y2row + i, v);
+        if (y2_bias) {
+          gn_ld<V>(y2_bias + i, t);
+#pragma unroll
+          for (int e = 0; e < V; ++e) v[e] += t[e];
+        }
+        gn_st<V>(buf2 + i, v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) ss2 += v[e] * v[e];
       }
     }
     float inv1 = 1.f, inv2 = 1.f;
@@ -108,57 +165,121 @@ __global__ void grouped_normed_add_kernel(
       if (y_gain) inv1 = rsqrtf(ss1 / (float)H + eps_branch);
       if (y2row && y2_gain) inv2 = rsqrtf(ss2 / (float)H + eps_branch);
     }
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      float z = y_scale * (y_gain ? y_gain[i] * (buf[i] * inv1) : buf[i]);
-      if (y2row) z += y2_scale * (y2_gain ? y2_gain[i] * (buf2[i] * inv2) : buf2[i]);
-      buf[i] = z;
+    for (int i = i0; i < H; i += di) {
+      float a[V], b[V], t[V];
+      gn_ld<V>(buf + i, a);
+      if (y_gain) {
+        gn_ld<V>(y_gain + i, t);
+#pragma unroll
+        for (int e = 0; e < V; ++e) a[e] = t[e] * (a[e] * inv1);
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) a[e] *= y_scale;
+      if (y2row) {
+        gn_ld<V>(buf2 + i, b);
+        if (y2_gain) {
+          gn_ld<V>(y2_gain + i, t);
+#pragma unroll
+          for (int e = 0; e < V; ++e) b[e] = t[e] * (b[e] * inv2);
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) a[e] += y2_scale * b[e];
+      }
+      gn_st<V>(buf + i, a);
     }
     if (g != nullptr) {
-      gn_group_inv(buf, H, g_groups, eps_y, scratch, psum, ginv);
+      gn_group_inv<V>(buf, H, g_groups, eps_y, scratch, psum, ginv);
       const int gw = H / g_groups;
-      for (int i = threadIdx.x; i < H; i += blockDim.x) buf[i] = hrow[i] + g[i] * (buf[i] * ginv[i / gw]);
+      for (int i = i0; i < H; i += di) {
+        float z[V], x[V], t[V];
+        gn_ld<V>(buf + i, z);
+        gn_ld<V>(hrow + i, x);
+        gn_ld<V>(g + i, t);
+        const float inv = ginv[i / gw];            // the V elements lie in one group
+#pragma unroll
+        for (int e = 0; e < V; ++e) x[e] += t[e] * (z[e] * inv);
+        gn_st<V>(buf + i, x);
+      }
     } else {
-      for (int i = threadIdx.x; i < H; i += blockDim.x) buf[i] = hrow[i] + buf[i];
+      for (int i = i0; i < H; i += di) {
+        float z[V], x[V];
+        gn_ld<V>(buf + i, z);
+        gn_ld<V>(hrow + i, x);
+#pragma unroll
+        for (int e = 0; e < V; ++e) x[e] += z[e];
+        gn_st<V>(buf + i, x);
+      }
     }
   } else {
-    for (int i = threadIdx.x; i < H; i += blockDim.x) buf[i] = hrow[i];
+    for (int i = i0; i < H; i += di) {
+      float x[V];
+      gn_ld<V>(hrow + i, x);
+      gn_st<V>(buf + i, x);
+    }
   }
-  // every thread has touched the same elements of buf in each loop so far: they are its own
   if (hist != nullptr) {
-    // the weights of the sum once into shared memory; the earlier results of an element are asked for eight at a
+    // the weights of the sum once into shared memory; the earlier results of an element are asked for several at a
     // time before any of them is used (the additions stay in the order j = 0, 1, ...)
     __syncthreads();
     for (int j = threadIdx.x; j <= n_hist; j += blockDim.x) psum[j] = dwa[j];
     __syncthreads();
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      const float x = buf[i];
+    constexpr int AHEAD = V == 4 ? 4 : 8;
+    for (int i = i0; i < H; i += di) {
+      float x[V], acc[V];
+      gn_ld<V>(buf + i, x);
       float* hp = hist + (size_t)tok * H + i;
-      hp[(size_t)n_hist * hist_stride] = x;
-      float acc = 0.f;
-      for (int j0 = 0; j0 < n_hist; j0 += 8) {
-        float v[8];
+      gn_st<V>(hp + (size_t)n_hist * hist_stride, x);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = j0 + u < n_hist ? hp[(size_t)(j0 + u) * hist_stride] : 0.f;
+      for (int e = 0; e < V; ++e) acc[e] = 0.f;
+      for (int j0 = 0; j0 < n_hist; j0 += AHEAD) {
+        float v[AHEAD][V];
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (j0 + u < n_hist) acc += psum[j0 + u] * v[u];
+        for (int u = 0; u < AHEAD; ++u) {
+          if (j0 + u < n_hist) gn_ld<V>(hp + (size_t)(j0 + u) * hist_stride, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u) {
+          if (j0 + u < n_hist) {
+            const float wj = psum[j0 + u];
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] += wj * v[u][e];
+          }
+        }
       }
-      acc += psum[n_hist] * x;
-      buf[i] = acc;
+      const float wl = psum[n_hist];
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc[e] += wl * x[e];
+      gn_st<V>(buf + i, acc);
     }
   }
   if (store_h && (y != nullptr || hist != nullptr)) {
-    for (int i = threadIdx.x; i < H; i += blockDim.x) hrow[i] = buf[i];
+    for (int i = i0; i < H; i += di) {
+      float x[V];
+      gn_ld<V>(buf + i, x);
+      gn_st<V>(hrow + i, x);
+    }
   }
   if (out == nullptr) return;
   O* orow = out + (size_t)r * H;
   if (w == nullptr) {
-    for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = qb_from_float<O>(buf[i]);
+    for (int i = i0; i < H; i += di) {
+      float x[V];
+      gn_ld<V>(buf + i, x);
+      gn_st_out<O, V>(orow + i, x);
+    }
     return;
   }
-  gn_group_inv(buf, H, w_groups, eps, scratch, psum, ginv);
+  gn_group_inv<V>(buf, H, w_groups, eps, scratch, psum, ginv);
   const int gw = H / w_groups;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = qb_from_float<O>(w[i] * (buf[i] * ginv[i / gw]));
+  for (int i = i0; i < H; i += di) {
+    float x[V], t[V];
+    gn_ld<V>(buf + i, x);
+    gn_ld<V>(w + i, t);
+    const float inv = ginv[i / gw];
+#pragma unroll
+    for (int e = 0; e < V; ++e) x[e] = t[e] * (x[e] * inv);
+    gn_st_out<O, V>(orow + i, x);
+  }
 }
 
 static bool gn_groups_ok(int H, int G) {
@@ -176,17 +297,29 @@ extern "C" int qb_grouped_normed_add(
   if ((g != nullptr && !gn_groups_ok(H, g_groups)) || (w != nullptr && !gn_groups_ok(H, w_groups))) return QB_ERR_UNSUPPORTED;
   const size_t smem = (size_t)(2 * H + 64 + GN_MAX_CHUNKS + GN_MAX_GROUPS) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
-  const int threads = H >= 2048 ? 512 : 256;
+  // 16-byte moves where every piece starts on such a boundary and lies within one group
+  auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = H % 4 == 0 && (g == nullptr || (H / g_groups) % 4 == 0) && (w == nullptr || (H / w_groups) % 4 == 0) &&
+                   al16(h) && al16(y) && al16(y_bias) && al16(y_gain) && al16(y2) && al16(y2_bias) && al16(y2_gain) && al16(g) &&
+                   al16(hist) && al16(w) && al16(out) && (hist == nullptr || hist_stride % 4 == 0);
+  const int per = vec ? 4 : 1;
+  const int threads = H >= 2048 * per ? 512 : 256;
+#define GN_LAUNCH(O, V)                                                                                              \
+  do {                                                                                                               \
+    auto kern = grouped_normed_add_kernel<O, V>;                                                                     \
+    if (smem > 48 * 1024) {                                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+      if (e != cudaSuccess) return (int)e;                                                                           \
+    }                                                                                                                \
+    kern<<<n_rows, threads, smem, stream>>>(h, y, S, y_scale, y_bias, y_gain, y2, y2_scale, y2_bias, y2_gain, eps_branch, \
+                                            g, g_groups, eps_y, hist, (size_t)hist_stride, n_hist, dwa, w, w_groups, eps, \
+                                            (O*)out, rows, n_rows, H, store_h);                                      \
+  } while (0)
   QB_DISPATCH_DTYPE(out_dtype, O, {
-    auto kern = grouped_normed_add_kernel<O>;
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    kern<<<n_rows, threads, smem, stream>>>(h, y, S, y_scale, y_bias, y_gain, y2, y2_scale, y2_bias, y2_gain, eps_branch,
-                                            g, g_groups, eps_y, hist, (size_t)hist_stride, n_hist, dwa, w, w_groups, eps,
-                                            (O*)out, rows, n_rows, H, store_h);
+    if (vec) GN_LAUNCH(O, 4);
+    else GN_LAUNCH(O, 1);
   });
+#undef GN_LAUNCH
   QB_LAUNCH_CHECK();
   return 0;
 }
