@@ -15,7 +15,9 @@ with the float32 copy of ``W_dt``; its bias and softplus are applied inside the 
 or with ``left_norm`` / ``right_norm`` ``left_scale * norm_l(left) + right_scale * norm_r(right)`` (each branch
 RMS-normed over the whole width with a gain of its own first).  Their caches and states live side by side (stream
 and state names must differ); the sum, and the branch norms, are left to the norm kernel that reads the mixer's
-output when the block has one.
+output when the block has one.  The two branches share nothing but their input, so the right one runs on a second
+CUDA stream beside the left one (``concurrent``; the streams fork and join inside the launch order, also in a captured
+step): an attention that fills the SMs and a recurrence that is a chain in time with few warps overlap.
 """
 
 from __future__ import annotations
@@ -85,8 +87,11 @@ class SelectiveScan(Mixer):
 class ParallelMixers(Mixer):
     graph_safe = True
 
+    _side_streams: dict = {}          # device index -> the stream the right branches run on
+
     def __init__(self, left, right, left_scale: float = 1.0, right_scale: float = 1.0, left_norm=None,
-                 right_norm=None):
+                 right_norm=None, concurrent: bool = True):
+        self.concurrent = bool(concurrent)
         self.left, self.right = make("mixer", left), make("mixer", right)
         self.left_scale, self.right_scale = float(left_scale), float(right_scale)
         self.left_norm = make("norm", left_norm) if left_norm is not None else None
@@ -118,8 +123,19 @@ class ParallelMixers(Mixer):
         return spec
 
     def forward(self, x, ctx, cache, state):
-        a = self.left.forward(x, ctx, cache, state)
-        b = self.right.forward(x, ctx, cache, state)
+        if self.concurrent and x.is_cuda:
+            main = torch.cuda.current_stream(x.device)
+            side = self._side_streams.get(x.device.index)
+            if side is None:
+                side = self._side_streams[x.device.index] = torch.cuda.Stream(device=x.device)
+            side.wait_stream(main)                      # the input, the cache and the state are as the launch order left them
+            with torch.cuda.stream(side):
+                b = self.right.forward(x, ctx, cache, state)
+            a = self.left.forward(x, ctx, cache, state)
+            main.wait_stream(side)                      # whoever reads the sum comes after both
+        else:
+            a = self.left.forward(x, ctx, cache, state)
+            b = self.right.forward(x, ctx, cache, state)
         a = a if isinstance(a, Addends) else Addends(a)
         b = b if isinstance(b, Addends) else Addends(b)
         if a.extra is not None or a.y.dim() != 2 or a.branch_normed or (self.left_norm is not None and a.scale != 1.0):
