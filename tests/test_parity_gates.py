@@ -9,7 +9,8 @@ GATES = _gates.discover()
 
 
 def test_the_gates_are_found():
-    assert {"minimax_m3_config_test", "minimax_m3_cuttings_test", "minimax_m3_generate_test", "tirizen_generate_test"} <= set(GATES)
+    assert {"minimax_m3_config_test", "minimax_m3_cuttings_test", "minimax_m3_generate_test", "tirizen_generate_test",
+            "puvolix_generate_test"} <= set(GATES)
 
 
 @pytest.mark.parametrize("name", [n for n, gpu in GATES.items() if not gpu])
