@@ -437,7 +437,7 @@ def plain_attn(tokens_per_req: int, reqs: int, context: int, nq: int, nkv: int, 
     pos = torch.arange(context - tokens_per_req, context, dtype=torch.int32, device=dev).repeat(reqs)
     req = torch.arange(reqs, dtype=torch.int32, device=dev).repeat_interleave(tokens_per_req)
     st = k.new_status(dev)
-    n_split = max(1, min(-(-8192 // (T * nkv)), -(-context // 32), 64))       # as parts/attention.py chooses it
+    n_split = max(1, min(-(-2048 // (T * nkv)), -(-context // 32), 256))      # as parts/attention.py chooses it
 
     def all_layers():
         for kc, vc in caches:
