@@ -214,7 +214,9 @@ def _attend(cache, q, pos, req, scale, dtype, **opts):
     (4, 2, 12, 20, 8, 4, torch.float32), (8, 2, 48, 32, 32, 16, torch.bfloat16), (6, 3, 16, 16, 0, 8, torch.float32),
     (2, 2, 64, 64, 32, 16, torch.bfloat16), (3, 1, 10, 6, 10, 5, torch.float32), (4, 1, 96, 64, 64, 16, torch.bfloat16),
     (2, 1, 128, 128, 128, 8, torch.bfloat16), (4, 2, 80, 16, 16, 16, torch.bfloat16), (4, 4, 32, 128, 0, 16, torch.bfloat16),
-    (2, 1, 256, 128, 64, 16, torch.bfloat16), (4, 2, 24, 40, 24, 16, torch.bfloat16), (2, 1, 144, 144, 48, 16, torch.bfloat16)])
+    (2, 1, 256, 128, 64, 16, torch.bfloat16), (4, 2, 24, 40, 24, 16, torch.bfloat16), (2, 1, 144, 144, 48, 16, torch.bfloat16),
+    (6, 2, 32, 32, 16, 16, torch.bfloat16), (5, 1, 64, 32, 64, 8, torch.bfloat16), (12, 4, 16, 48, 8, 16, torch.bfloat16),
+    (7, 7, 48, 16, 48, 16, torch.bfloat16), (20, 1, 32, 32, 32, 16, torch.bfloat16)])
 def test_attention_of_prompts_portions_and_single_tokens(nq, G, hd, vd, dims, page, dtype):
     """Two sequences: the first as one prompt, the second as a portion and then token by token, through shuffled
     pages; per-head norm gains, rotated part, head temperatures and scale as the plain functions have them."""
