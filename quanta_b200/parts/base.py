@@ -209,6 +209,30 @@ class Part:
         return []
 
 
+_SIDE_STREAMS: dict = {}          # device index -> the second stream of that device
+
+
+def run_beside(side_fn, main_fn, device):
+    """Two pieces of work that share nothing but their inputs, ``side_fn()`` on a second CUDA stream beside
+    ``main_fn()`` on the current one; returns ``(side result, main result)``.  The streams fork and join inside the
+    launch order (the second stream waits for everything launched so far, the current one then waits for it), also in
+    a captured step; what the side work allocates is used afterwards on the current stream only behind that join, and
+    the next fork comes behind the current stream's use of it.  Not on a CUDA device: one after the other."""
+    if torch.device(device).type != "cuda":
+        return side_fn(), main_fn()
+    dev = torch.device(device)
+    main = torch.cuda.current_stream(dev)
+    side = _SIDE_STREAMS.get(dev.index)
+    if side is None:
+        side = _SIDE_STREAMS[dev.index] = torch.cuda.Stream(device=dev)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        b = side_fn()
+    a = main_fn()
+    main.wait_stream(side)
+    return b, a
+
+
 class Addends:
     """A sublayer's output as a sum that nobody has taken yet:
     ``scale * n_y(sum_s y[:, s] + bias) + extra_scale * n_e(extra + extra_bias)`` with ``y`` float32 ``[T, H]`` or

@@ -18,7 +18,7 @@ import os
 import torch
 
 from .. import kernels
-from .base import Addends, FeedForward, TensorSpec, register
+from .base import Addends, FeedForward, TensorSpec, register, run_beside
 
 
 @register("feed_forward", "sigmoid_topk_experts")
@@ -288,10 +288,11 @@ class SoftmaxSharedExperts(SigmoidTopKExperts):
             self.gate_pieces = kernels.split3_bf16(self.gate_w)
 
     def forward(self, x, ctx):
-        y = super().forward(x, ctx)
         if self.shared is None:
-            return Addends(y)
-        return Addends(y, extra=self.shared.forward(x, ctx))
+            return Addends(super().forward(x, ctx))
+        routed = super().forward
+        extra, y = run_beside(lambda: self.shared.forward(x, ctx), lambda: routed(x, ctx), x.device)
+        return Addends(y, extra=extra)
 
 
 @register("feed_forward", "input_weighted_experts")
@@ -325,8 +326,9 @@ class InputWeightedExperts(SigmoidTopKExperts):
         return [self.shared] if self.shared is not None else []
 
     def forward(self, x, ctx):
-        y = super().forward(x, ctx)
         if self.shared is None:
-            return Addends(y)
-        extra = self.shared.forward(x, ctx)
+            return Addends(super().forward(x, ctx))
+        # the shared expert reads the same rows and nothing of the routed ones: it runs beside them
+        routed = super().forward
+        extra, y = run_beside(lambda: self.shared.forward(x, ctx), lambda: routed(x, ctx), x.device)
         return Addends(y, extra=extra.y if isinstance(extra, Addends) else extra)

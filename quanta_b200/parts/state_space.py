@@ -26,7 +26,7 @@ import torch
 
 from .. import kernels
 from ..matmul import empty_rows, linear
-from .base import Addends, Mixer, TensorSpec, make, register
+from .base import Addends, Mixer, TensorSpec, make, register, run_beside
 
 
 @register("mixer", "selective_scan")
@@ -87,8 +87,6 @@ class SelectiveScan(Mixer):
 class ParallelMixers(Mixer):
     graph_safe = True
 
-    _side_streams: dict = {}          # device index -> the stream the right branches run on
-
     def __init__(self, left, right, left_scale: float = 1.0, right_scale: float = 1.0, left_norm=None,
                  right_norm=None, concurrent: bool = True):
         self.concurrent = bool(concurrent)
@@ -124,15 +122,8 @@ class ParallelMixers(Mixer):
 
     def forward(self, x, ctx, cache, state):
         if self.concurrent and x.is_cuda:
-            main = torch.cuda.current_stream(x.device)
-            side = self._side_streams.get(x.device.index)
-            if side is None:
-                side = self._side_streams[x.device.index] = torch.cuda.Stream(device=x.device)
-            side.wait_stream(main)                      # the input, the cache and the state are as the launch order left them
-            with torch.cuda.stream(side):
-                b = self.right.forward(x, ctx, cache, state)
-            a = self.left.forward(x, ctx, cache, state)
-            main.wait_stream(side)                      # whoever reads the sum comes after both
+            b, a = run_beside(lambda: self.right.forward(x, ctx, cache, state),
+                              lambda: self.left.forward(x, ctx, cache, state), x.device)
         else:
             a = self.left.forward(x, ctx, cache, state)
             b = self.right.forward(x, ctx, cache, state)
